@@ -1,0 +1,194 @@
+/*
+ * infmoe_c.h -- C ABI of the B200-native MoE layer (libinfmoe_b200.so).
+ *
+ * Everything the TensorRT-facing plugin classes (MoELayerPlugin /
+ * MoELayerPluginCreator) and the Python binding need is reached through the
+ * entry points below: plain pointers and sizes, no C++ or framework types.
+ * Each declaration names the reference interface it replaces (paths are
+ * relative to the InfMoE repository root).
+ *
+ * Conventions
+ *   - every function returns an infmoe_status (0 = ok) and never exits or
+ *     throws; infmoe_last_error() gives a thread-local message;
+ *   - pointers named d_* are device pointers on the current CUDA device,
+ *     h_* are host pointers; `stream` is a cudaStream_t passed as void*;
+ *   - all tensors are FP32, row-major, indices are int32;
+ *   - work is ordered on `stream`; unless a function says so it does not
+ *     block the host.
+ */
+#ifndef INFMOE_C_H
+#define INFMOE_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INFMOE_API __attribute__((visibility("default")))
+
+typedef enum infmoe_status {
+    INFMOE_OK = 0,
+    INFMOE_ERR_INVALID_ARGUMENT = 1, /* reference: assert(false) after a message on stderr */
+    INFMOE_ERR_CUDA = 2,             /* reference: CUDA_SAFE_CALL -> exit(-1), plugin/utility.h:15-21 */
+    INFMOE_ERR_NAN = 3,              /* a token selected no expert; reference: device assert, plugin/cuda/moe.cu:70 */
+    INFMOE_ERR_IO = 4,               /* weight file missing / unreadable */
+    INFMOE_ERR_FORMAT = 5,           /* npz / serialised blob malformed, wrong shapes or dtypes */
+    INFMOE_ERR_UNSUPPORTED = 6,
+    INFMOE_ERR_DEVICE_TIMEOUT = 7,   /* a bounded device-side wait ran out */
+    INFMOE_ERR_STATE = 8             /* call order violated (e.g. enqueue before initialize) */
+} infmoe_status;
+
+/* Thread-local description of the last non-zero status returned on this thread. */
+INFMOE_API const char* infmoe_last_error(void);
+
+/* ------------------------------------------------------------------------ */
+/* Layer object = what MoELayerPlugin holds (plugin/MoELayerPlugin.h:45-80)  */
+/* ------------------------------------------------------------------------ */
+typedef struct infmoe_layer infmoe_layer;
+
+/* The nine plugin attributes, plugin/MoELayerPluginCreator.cc:15-47 (parsed at :75-115). */
+typedef struct infmoe_layer_config {
+    int32_t expert_count;
+    int32_t embedding_size;            /* d_model */
+    int32_t hidden_size;               /* d_ff */
+    int32_t max_concurrency;           /* number of device weight slots when experts are streamed; default 2 */
+    const float* expert_centroids;     /* host, [expert_count][embedding_size] row-major (MoELayerPlugin.cc:334-336) */
+    const float* layernorm_weight;     /* host, [embedding_size]; required iff moe_variant == "cpm_2" */
+    const char* expert_weight_file;    /* npz path; may be NULL if weights are given with infmoe_layer_set_expert */
+    const char* expert_sublayer_type;  /* "T5_FF" or "Identity" */
+    const char* moe_variant;           /* "cpm_2", "base_layer" or "default" */
+} infmoe_layer_config;
+
+/* MoELayerPluginCreator::createPlugin + MoELayerPlugin main constructor
+ * (plugin/MoELayerPluginCreator.cc:58-148, plugin/MoELayerPlugin.cc:60-81).
+ * Copies the arrays and strings.  No device work. */
+INFMOE_API int infmoe_layer_create(const infmoe_layer_config* cfg, infmoe_layer** out);
+
+/* MoELayerPlugin::clone (plugin/MoELayerPlugin.cc:83-102,465-468): deep-copies
+ * centroids / layernorm weight, shares the expert weights. */
+INFMOE_API int infmoe_layer_clone(const infmoe_layer* src, infmoe_layer** out);
+
+/* MoELayerPlugin::initialize -> T5FFLayer::initialize (plugin/sublayers/T5FFLayer.cc:143-147):
+ * reads the whole npz into pinned host memory.  Keys "{n}/layer_norm_weight",
+ * "{n}/wi_0_weight", "{n}/wi_1_weight", "{n}/wo_weight" (T5FFLayer.cc:55-88). */
+INFMOE_API int infmoe_layer_initialize(infmoe_layer* layer);
+
+/* Gives one expert's weights by pointer instead of through the npz (host or
+ * device pointers; they are copied).  ln_w [D], wi0/wi1 [F][D], wo [D][F].
+ * With on_device != 0 the data is taken from device memory straight into the
+ * resident device store (no host copy is kept).  No reference counterpart: the
+ * reference only reads npz files. */
+INFMOE_API int infmoe_layer_set_expert(infmoe_layer* layer, int32_t expert, const float* ln_w, const float* wi0,
+                                       const float* wi1, const float* wo, int on_device);
+
+/* Residency of expert weights.  mode 0: stream every used expert from pinned
+ * host memory on every call through max_concurrency slots, like the reference
+ * (plugin/MoELayerPlugin.cc:360-394); mode 1: keep all experts in device
+ * memory owned by the layer; mode -1: choose 1 when they fit. */
+INFMOE_API int infmoe_layer_set_residency(infmoe_layer* layer, int mode);
+
+/* MoELayerPlugin::getWorkspaceSize (plugin/MoELayerPlugin.cc:253-273) for token_num = B * S. */
+INFMOE_API int infmoe_layer_workspace_bytes(const infmoe_layer* layer, int64_t token_num, size_t* bytes);
+
+/* MoELayerPlugin::enqueue (plugin/MoELayerPlugin.cc:279-416).  d_input and
+ * d_output are [token_num][embedding_size] and must not alias.  The status of
+ * device-side checks (NaN routing, bounded waits) of this call is returned by
+ * the next infmoe_layer_sync_status. */
+INFMOE_API int infmoe_layer_enqueue(infmoe_layer* layer, const float* d_input, float* d_output, void* d_workspace,
+                                    size_t workspace_bytes, int64_t token_num, void* stream);
+
+/* Blocks until `stream` is idle and returns the device-side status of the calls enqueued so far. */
+INFMOE_API int infmoe_layer_sync_status(infmoe_layer* layer, void* stream);
+
+/* Host-buffer convenience: copies h_input to the device, runs enqueue with an
+ * internally owned workspace, copies the result to h_output and waits.  This
+ * is the end-to-end call the benchmark times. */
+INFMOE_API int infmoe_layer_forward_host(infmoe_layer* layer, const float* h_input, float* h_output,
+                                         int64_t token_num);
+
+/* Routing/dispatch results of the last enqueue (device pointers inside the
+ * workspace of that call; valid until the next enqueue).  Any out pointer may be NULL. */
+INFMOE_API int infmoe_layer_last_routing(const infmoe_layer* layer, const int32_t** d_gate, const float** d_score,
+                                         const int32_t** d_pos, const int32_t** d_count, const int32_t** d_offset);
+
+/* Number of kernels this library launched on behalf of `layer` so far. */
+INFMOE_API int64_t infmoe_layer_kernel_launches(const infmoe_layer* layer);
+
+/* MoELayerPlugin::terminate + destructor (plugin/MoELayerPlugin.cc:203-237). */
+INFMOE_API int infmoe_layer_destroy(infmoe_layer* layer);
+
+/* MoELayerPlugin::getSerializationSize / serialize / deserialising constructor
+ * (plugin/MoELayerPlugin.cc:418-458, :104-143).  Same fields in the same order,
+ * in a self-consistent versioned blob. */
+INFMOE_API int infmoe_layer_serialization_size(const infmoe_layer* layer, size_t* bytes);
+INFMOE_API int infmoe_layer_serialize(const infmoe_layer* layer, void* h_buffer, size_t bytes);
+INFMOE_API int infmoe_layer_deserialize(const void* h_buffer, size_t bytes, infmoe_layer** out);
+
+/* Walks an expert weight file exactly like infmoe_layer_initialize (same reader,
+ * same key and size checks as plugin/sublayers/T5FFLayer.cc:55-88) without
+ * keeping the data or touching CUDA.  h_sums (may be NULL) receives, per expert,
+ * the double-precision sums of its four tensors in the order layer_norm, wi_0,
+ * wi_1, wo: [expert_count][4]. */
+INFMOE_API int infmoe_weight_file_check(const char* path, int32_t expert_count, int32_t embedding_size,
+                                        int32_t hidden_size, double* h_sums);
+
+/* Read-back of the attributes (for the plugin classes and the Python binding). */
+INFMOE_API int infmoe_layer_get_config(const infmoe_layer* layer, infmoe_layer_config* out);
+
+/* ------------------------------------------------------------------------ */
+/* Stage entry points = the free functions of plugin/cuda/moe.h and ops.h     */
+/* ------------------------------------------------------------------------ */
+
+/* Fused routing: [cpm_2 LayerNorm, plugin/MoELayerPlugin.cc:315-327] + gating
+ * scores [cublasSgemm_v2, :334-336] + top-1 [moe_expert_select, plugin/cuda/moe.cu:147-159].
+ * d_ln_w == NULL skips the LayerNorm.  d_status (int32, may be NULL) gets bit 0
+ * set when a token selects no expert. */
+INFMOE_API int infmoe_route(const float* d_x, const float* d_centroids, const float* d_ln_w, int64_t token_num,
+                            int32_t embedding_size, int32_t expert_count, int32_t* d_gate, float* d_score,
+                            int32_t* d_status, void* stream);
+
+/* moe_expert_select (plugin/cuda/moe.cu:147-159): top-1 over a given score matrix [T][E]. */
+INFMOE_API int infmoe_expert_select(int64_t token_num, int32_t expert_count, const float* d_aff, int32_t* d_gate,
+                                    float* d_weight, int32_t* d_status, void* stream);
+
+/* moe_expert_count (plugin/cuda/moe.cu:161-212), on the device: d_count[E],
+ * d_offset[E+1] (offset[E] = T, plugin/MoELayerPlugin.cc:351), d_pos[T] in the
+ * reference's stable order. */
+INFMOE_API int infmoe_expert_count(int64_t token_num, int32_t expert_count, const int32_t* d_gate, int32_t* d_pos,
+                                   int32_t* d_count, int32_t* d_offset, int32_t* d_status, void* stream);
+
+/* moe_expert_scatter (plugin/cuda/moe.cu:214-228). d_coeff / d_routed_coeff may be NULL. */
+INFMOE_API int infmoe_expert_scatter(int64_t token_num, int32_t token_len, const float* d_input,
+                                     const float* d_coeff, const int32_t* d_pos, float* d_routed,
+                                     float* d_routed_coeff, void* stream);
+
+/* moe_expert_gather (plugin/cuda/moe.cu:230-240). */
+INFMOE_API int infmoe_expert_gather(int64_t token_num, int32_t token_len, const float* d_routed,
+                                    const int32_t* d_pos, float* d_output, void* stream);
+
+/* moe_expert_base_layer_fused_mix_and_gather (plugin/cuda/moe.cu:242-258). */
+INFMOE_API int infmoe_expert_mix_gather(int64_t token_num, int32_t token_len, const int32_t* d_pos,
+                                        const float* d_routed, const float* d_post, const float* d_coeff,
+                                        float* d_output, void* stream);
+
+/* layernorm_gpu<float,float> with gamma, no beta, eps 1e-6 (plugin/cuda/ops/layernorm.cu:179-188). */
+INFMOE_API int infmoe_layernorm(float* d_out, const float* d_in, int64_t rows, int32_t cols, const float* d_gamma,
+                                void* stream);
+
+/* fused_gelu_dot_gpu<float> (plugin/cuda/ops/gelu.cu:18-25): B = gelu(A) * B. */
+INFMOE_API int infmoe_gelu_dot(const float* d_a, float* d_b, size_t len, void* stream);
+
+/* T5FFLayer::run for one expert (plugin/sublayers/T5FFLayer.cc:90-141) on
+ * `rows` rows: d_y = d_x + (gelu(LN(x) wi0^T) * (LN(x) wi1^T)) wo^T.  Weights are
+ * plain FP32 device arrays.  d_workspace must hold infmoe_t5ff_workspace_bytes. */
+INFMOE_API int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t embedding_size, int32_t hidden_size, size_t* bytes);
+INFMOE_API int infmoe_t5ff_run(int64_t rows, int32_t embedding_size, int32_t hidden_size, const float* d_ln_w,
+                               const float* d_wi0, const float* d_wi1, const float* d_wo, const float* d_x,
+                               float* d_y, void* d_workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFMOE_C_H */

@@ -1,0 +1,114 @@
+"""ctypes binding of the C ABI declared in include/infmoe_c.h.
+
+The library is loaded from the package directory; there is no fallback: if
+libinfmoe_b200.so is missing or fails to load, importing the symbols raises.
+Device pointers are passed as plain integers (e.g. ``tensor.data_ptr()``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libinfmoe_b200.so")
+
+STATUS_NAMES = {
+    0: "INFMOE_OK",
+    1: "INFMOE_ERR_INVALID_ARGUMENT",
+    2: "INFMOE_ERR_CUDA",
+    3: "INFMOE_ERR_NAN",
+    4: "INFMOE_ERR_IO",
+    5: "INFMOE_ERR_FORMAT",
+    6: "INFMOE_ERR_UNSUPPORTED",
+    7: "INFMOE_ERR_DEVICE_TIMEOUT",
+    8: "INFMOE_ERR_STATE",
+}
+
+
+class InfMoEError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+
+
+class LayerConfig(ctypes.Structure):
+    """struct infmoe_layer_config"""
+
+    _fields_ = [
+        ("expert_count", ctypes.c_int32),
+        ("embedding_size", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("max_concurrency", ctypes.c_int32),
+        ("expert_centroids", ctypes.POINTER(ctypes.c_float)),
+        ("layernorm_weight", ctypes.POINTER(ctypes.c_float)),
+        ("expert_weight_file", ctypes.c_char_p),
+        ("expert_sublayer_type", ctypes.c_char_p),
+        ("moe_variant", ctypes.c_char_p),
+    ]
+
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int32
+_sz = ctypes.c_size_t
+
+# name -> argument types (every function returns int unless listed in _RESTYPES)
+SIGNATURES = {
+    "infmoe_layer_create": [ctypes.POINTER(LayerConfig), ctypes.POINTER(_vp)],
+    "infmoe_layer_clone": [_vp, ctypes.POINTER(_vp)],
+    "infmoe_layer_initialize": [_vp],
+    "infmoe_layer_set_expert": [_vp, _i32, _vp, _vp, _vp, _vp, ctypes.c_int],
+    "infmoe_layer_set_residency": [_vp, ctypes.c_int],
+    "infmoe_layer_workspace_bytes": [_vp, _i64, ctypes.POINTER(_sz)],
+    "infmoe_layer_enqueue": [_vp, _vp, _vp, _vp, _sz, _i64, _vp],
+    "infmoe_layer_sync_status": [_vp, _vp],
+    "infmoe_layer_forward_host": [_vp, _vp, _vp, _i64],
+    "infmoe_layer_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,
+    "infmoe_layer_kernel_launches": [_vp],
+    "infmoe_layer_destroy": [_vp],
+    "infmoe_layer_serialization_size": [_vp, ctypes.POINTER(_sz)],
+    "infmoe_layer_serialize": [_vp, _vp, _sz],
+    "infmoe_layer_deserialize": [_vp, _sz, ctypes.POINTER(_vp)],
+    "infmoe_layer_get_config": [_vp, ctypes.POINTER(LayerConfig)],
+    "infmoe_weight_file_check": [ctypes.c_char_p, _i32, _i32, _i32, _vp],
+    "infmoe_route": [_vp, _vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp],
+    "infmoe_expert_select": [_i64, _i32, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_expert_count": [_i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_expert_scatter": [_i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_expert_gather": [_i64, _i32, _vp, _vp, _vp, _vp],
+    "infmoe_expert_mix_gather": [_i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_layernorm": [_vp, _vp, _i64, _i32, _vp, _vp],
+    "infmoe_gelu_dot": [_vp, _vp, _sz, _vp],
+    "infmoe_t5ff_workspace_bytes": [_i64, _i32, _i32, ctypes.POINTER(_sz)],
+    "infmoe_t5ff_run": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],
+    "infmoe_last_error": [],
+}
+_RESTYPES = {"infmoe_last_error": ctypes.c_char_p, "infmoe_layer_kernel_launches": ctypes.c_int64}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libinfmoe_b200.so and declares every entry point of infmoe_c.h."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m infmoe_b200.build` (there is no CPU fallback)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(handle, name)  # raises AttributeError if a declared symbol is not exported
+            fn.argtypes = args
+            fn.restype = _RESTYPES.get(name, ctypes.c_int)
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    msg = lib().infmoe_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise InfMoEError(status, last_error())

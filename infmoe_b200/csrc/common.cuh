@@ -1,0 +1,122 @@
+// Shared host/device helpers of the B200 MoE-layer kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+#include <cstdio>
+
+#include "infmoe_c.h"
+
+namespace infmoe {
+
+// ---------------------------------------------------------------------------
+// Error plumbing: nothing in this library exits the process (the reference's
+// CUDA_SAFE_CALL does, plugin/utility.h:15-21); every failure becomes a status.
+// ---------------------------------------------------------------------------
+void set_error(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+
+#define INFMOE_CUDA_TRY(call)                                                                              \
+    do {                                                                                                   \
+        cudaError_t err__ = (call);                                                                        \
+        if (err__ != cudaSuccess) {                                                                        \
+            ::infmoe::set_error("CUDA error %d (%s) at %s:%d", (int)err__, cudaGetErrorString(err__),      \
+                                __FILE__, __LINE__);                                                       \
+            return INFMOE_ERR_CUDA;                                                                        \
+        }                                                                                                  \
+    } while (0)
+
+#define INFMOE_TRY(call)                \
+    do {                                \
+        int rc__ = (call);              \
+        if (rc__ != INFMOE_OK) return rc__; \
+    } while (0)
+
+// Bits of the device-side status word.
+enum : int32_t {
+    STATUS_NO_EXPERT = 1,      // a token selected no expert (NaN scores)
+    STATUS_BAD_GATE = 2,       // gate index outside [0, E)
+    STATUS_WAIT_TIMEOUT = 4,   // a bounded mbarrier wait ran out inside a GEMM kernel
+    STATUS_BAD_SHAPE = 8,
+};
+
+// Process-wide count of kernels launched by this library.
+extern long long g_kernel_launches;
+inline void note_launch(int n = 1) { g_kernel_launches += n; }
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------
+// Canonical FP32 reductions.  Routing must agree bit for bit with the CPU
+// checker, so the summation order is fixed: lane l of a warp owns elements
+// k = 4*(l + 32*i) + c (i ascending, c = 0..3), accumulates them in that order
+// with explicit round-to-nearest adds / fused multiply-adds, and the 32 lane
+// partials are combined by a butterfly (xor 16, 8, 4, 2, 1).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_xor_sum(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// Loads elements [base, base+4) of a row; `vec` says the row is 16-byte aligned
+// with D % 4 == 0.  Elements at or beyond D read as 0 and must be skipped by the caller.
+__device__ __forceinline__ float4 load_row4(const float* __restrict__ row, int base, int D, bool vec) {
+    if (vec) return *reinterpret_cast<const float4*>(row + base);
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (base + 0 < D) r.x = row[base + 0];
+    if (base + 1 < D) r.y = row[base + 1];
+    if (base + 2 < D) r.z = row[base + 2];
+    if (base + 3 < D) r.w = row[base + 3];
+    return r;
+}
+
+// LayerNorm statistics of one row held by a full warp (true LayerNorm: mean
+// subtracted, biased variance, eps 1e-6; reference plugin/cuda/ops/layernorm.cu:126-149).
+__device__ __forceinline__ void warp_row_stats(const float* __restrict__ row, int D, bool vec, float& mean,
+                                               float& rstd) {
+    const int lane = threadIdx.x & 31;
+    float s = 0.f;
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 v = load_row4(row, base, D, vec);
+        s = __fadd_rn(s, v.x);
+        if (base + 1 < D) s = __fadd_rn(s, v.y);
+        if (base + 2 < D) s = __fadd_rn(s, v.z);
+        if (base + 3 < D) s = __fadd_rn(s, v.w);
+    }
+    mean = __fdiv_rn(warp_xor_sum(s), (float)D);
+    float q = 0.f;
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 v = load_row4(row, base, D, vec);
+        float d = __fsub_rn(v.x, mean);
+        q = __fmaf_rn(d, d, q);
+        if (base + 1 < D) { d = __fsub_rn(v.y, mean); q = __fmaf_rn(d, d, q); }
+        if (base + 2 < D) { d = __fsub_rn(v.z, mean); q = __fmaf_rn(d, d, q); }
+        if (base + 3 < D) { d = __fsub_rn(v.w, mean); q = __fmaf_rn(d, d, q); }
+    }
+    const float var = __fdiv_rn(warp_xor_sum(q), (float)D);
+    rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-6f)));
+}
+
+// gamma * ((x - mean) * rstd), reference plugin/cuda/ops/layernorm.cu:158-161.
+__device__ __forceinline__ float ln_apply(float x, float mean, float rstd, float gamma) {
+    return __fmul_rn(gamma, __fmul_rn(__fsub_rn(x, mean), rstd));
+}
+
+// Splits an FP32 value into a TF32-representable head and an FP32 remainder:
+// hi = x rounded to 10 mantissa bits (round to nearest, ties away), lo = x - hi (exact).
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    lo = __fsub_rn(x, hi);
+}
+
+// gelu(a) * b in the reference's evaluation order (plugin/cuda/ops/gelu.cu:8-15).
+__device__ __forceinline__ float gelu_dot(float a, float b) {
+    const float cdf = 0.5f * (1.0f + tanhf(a * (0.035677408136300125f * a * a + 0.7978845608028654f)));
+    return a * cdf * b;
+}
+#endif  // __CUDACC__
+
+}  // namespace infmoe

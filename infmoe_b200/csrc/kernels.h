@@ -1,0 +1,42 @@
+// Launchers of the CUDA kernels (defined in route.cu, dispatch.cu, rows.cu, ffn_simt.cu, ffn_umma.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace infmoe {
+
+int launch_route(const float* X, const float* C, const float* gamma, long long T, int D, int E, int* gate,
+                 float* score, int* status, cudaStream_t stream);
+int launch_select_top1(long long T, int E, const float* aff, int* gate, float* weight, int* status,
+                       cudaStream_t stream);
+int launch_dispatch(const int* gate, long long T, int E, int* pos, int* count, int* offset, int* status,
+                    cudaStream_t stream);
+int launch_scatter(long long T, int D, const float* X, const float* coeff, const int* pos, float* routed,
+                   float* rcoeff, cudaStream_t stream);
+int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
+                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo,
+                            cudaStream_t stream);
+int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream);
+int launch_mix_gather(long long T, int D, const int* pos, const float* routed, const float* post,
+                      const float* coeff, float* out, cudaStream_t stream);
+int launch_layernorm(float* out, const float* in, long long n, int D, const float* gamma, cudaStream_t stream);
+int launch_gelu_dot(const float* a, float* b, size_t len, cudaStream_t stream);
+int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_t stream);
+int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
+                    cudaStream_t stream);
+
+int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
+                    const float* h_hi, const float* h_lo, const float* w0_hi, const float* w0_lo,
+                    const float* w1_hi, const float* w1_lo, const float* wo_hi, const float* wo_lo,
+                    const float* routed, float* g_hi, float* g_lo, float* post, cudaStream_t stream);
+
+bool ffn_umma_supported(int D, int F, int E);
+int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
+                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w0_hi,
+                    const float* w0_lo, const float* w1_hi, const float* w1_lo, const float* wo_hi,
+                    const float* wo_lo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
+                    int num_sms, cudaStream_t stream);
+
+}  // namespace infmoe

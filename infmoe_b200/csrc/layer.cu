@@ -1,0 +1,1049 @@
+// Host side of the B200 MoE layer: the layer object behind the C ABI
+// (include/infmoe_c.h), its expert-weight store, the max_concurrency weight
+// streaming scheduler and the stream-ordered forward pass.
+//
+// Reference counterparts:
+//   MoELayerPlugin ctor / clone / terminate   plugin/MoELayerPlugin.cc:60-102,203-237
+//   MoELayerPlugin::getWorkspaceSize          plugin/MoELayerPlugin.cc:253-273
+//   MoELayerPlugin::enqueue                   plugin/MoELayerPlugin.cc:279-416
+//   T5FFLayer::initialize / copyWeights       plugin/sublayers/T5FFLayer.cc:143-147,55-88
+//   serialize / deserialising ctor            plugin/MoELayerPlugin.cc:418-458,104-143
+//
+// Differences by design: the forward pass never blocks the host when the
+// experts are resident (the reference synchronises after every stage); when
+// experts are streamed from pinned host memory there is exactly one host
+// synchronisation per call (the per-expert token counts), after which copies
+// and GEMMs are chained with events only.
+#include <cstdarg>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include <sys/stat.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "npz.h"
+
+namespace infmoe {
+
+long long g_kernel_launches = 0;
+
+static thread_local char t_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+}
+
+namespace {
+
+constexpr size_t ALIGN = 256;
+inline size_t align_up(size_t x) { return (x + ALIGN - 1) / ALIGN * ALIGN; }
+
+// Behaviour flags of the three variants (plugin/MoELayerPlugin.h:36-42, parseFlags MoELayerPlugin.cc:44-58).
+struct Flags {
+    bool layernorm_before_score = false;  // cpm_2
+    bool base_layer_mix = false;          // base_layer
+};
+
+// Expert weights, shared by a layer and its clones like the reference's
+// shared_ptr<MoESubLayer> (plugin/MoELayerPlugin.cc:83-102).
+struct ExpertStore {
+    int E = 0, D = 0, F = 0;
+    std::mutex mu;
+    // pinned host copies of the raw FP32 weights (streaming mode source); nullptr if absent
+    std::vector<float*> h_ln, h_wi0, h_wi1, h_wo;
+    std::vector<char> on_host;
+    // device: LayerNorm weights of all experts [E][D] (always resident, 4*E*D bytes)
+    float* d_ln = nullptr;
+    std::vector<char> ln_on_device;
+    // device-resident TF32 head/tail planes: w0_hi, w0_lo, w1_hi, w1_lo, wo_hi, wo_lo, each [E][F*D]
+    float* d_plane[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    std::vector<char> on_device;
+    bool fortran_warning = false;
+
+    size_t matrix_elems() const { return (size_t)D * (size_t)F; }
+    size_t resident_bytes() const { return 6 * matrix_elems() * (size_t)E * sizeof(float); }
+
+    ~ExpertStore() {
+        for (auto& v : {&h_ln, &h_wi0, &h_wi1, &h_wo})
+            for (float* p : *v)
+                if (p) cudaFreeHost(p);
+        if (d_ln) cudaFree(d_ln);
+        for (float* p : d_plane)
+            if (p) cudaFree(p);
+    }
+};
+
+struct WsLayout {
+    size_t gate, pos, count, offset, slot_map, score, rscore, routed, post, h_hi, h_lo, g_hi, g_lo, slots, total;
+};
+
+}  // namespace
+}  // namespace infmoe
+
+using namespace infmoe;
+
+struct infmoe_layer {
+    int E = 0, D = 0, F = 0, mc = 2;
+    std::vector<float> centroids, gating_ln;
+    std::string weight_file, sublayer_type, variant;
+    Flags flags;
+    bool identity = false;
+    std::shared_ptr<ExpertStore> store;
+    int residency = -1;          // -1 auto, 0 streamed, 1 resident
+    bool residency_resolved = false;
+    bool resident = false;
+    bool initialized = false;
+    int ffn_path = 0;            // 0 tensor cores when the shape allows, 1 exact CUDA-core kernels
+
+    // device state, created at the first enqueue (reference: ensureCUDAContext / ensureGPUWeights,
+    // plugin/MoELayerPlugin.cc:182-195,14-26)
+    bool device_ready = false;
+    int device = -1, num_sms = 0;
+    float* d_centroids = nullptr;
+    float* d_gating_ln = nullptr;
+    int* d_status = nullptr;
+    int* h_status = nullptr;     // pinned
+    int* h_count = nullptr;      // pinned [E]
+    int* h_slot_map = nullptr;   // pinned [E]
+    std::vector<cudaStream_t> copy_streams;
+    std::vector<cudaEvent_t> ev_ready, ev_freed;
+    cudaEvent_t ev_fork = nullptr;
+
+    // results of the last enqueue
+    const int* last_gate = nullptr;
+    const float* last_score = nullptr;
+    const int* last_pos = nullptr;
+    const int* last_count = nullptr;
+    const int* last_offset = nullptr;
+
+    // buffers owned for infmoe_layer_forward_host
+    float* own_in = nullptr;
+    float* own_out = nullptr;
+    void* own_ws = nullptr;
+    size_t own_io_bytes = 0, own_ws_bytes = 0;
+    cudaStream_t own_stream = nullptr;
+
+    long long launches_at_create = 0;
+};
+
+namespace {
+
+int parse_flags(const char* variant, Flags* f) {
+    *f = Flags();
+    if (!variant) {
+        set_error("moe_variant is missing");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (strcmp(variant, "base_layer") == 0) f->base_layer_mix = true;
+    else if (strcmp(variant, "cpm_2") == 0) f->layernorm_before_score = true;
+    else if (strcmp(variant, "default") == 0) {}
+    else {
+        set_error("unsupported moe variant: %s", variant);  // plugin/MoELayerPlugin.cc:54-55
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    return INFMOE_OK;
+}
+
+WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
+    WsLayout w{};
+    size_t o = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = o;
+        o += align_up(bytes);
+        return at;
+    };
+    const size_t t = (size_t)T, D = (size_t)L->D, F = (size_t)L->F, E = (size_t)L->E;
+    w.gate = take(4 * t);
+    w.pos = take(4 * t);
+    w.count = take(4 * E);
+    w.offset = take(4 * (E + 1));
+    w.slot_map = take(4 * E);
+    w.score = take(4 * t);
+    w.rscore = take(4 * t);
+    w.routed = take(4 * t * D);
+    w.post = take(4 * t * D);
+    w.h_hi = take(4 * t * D);
+    w.h_lo = take(4 * t * D);
+    w.g_hi = take(4 * t * F);
+    w.g_lo = take(4 * t * F);
+    w.slots = take(streamed && !L->identity ? 6 * (size_t)L->mc * D * F * 4 : 0);
+    w.total = o;
+    return w;
+}
+
+int ensure_store_device_ln(ExpertStore* s) {
+    if (!s->d_ln) {
+        INFMOE_CUDA_TRY(cudaMalloc(&s->d_ln, sizeof(float) * (size_t)s->E * s->D));
+        // experts never given weights keep gamma = 1 so that stray rows stay finite
+        std::vector<float> ones((size_t)s->E * s->D, 1.0f);
+        INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln, ones.data(), sizeof(float) * ones.size(), cudaMemcpyHostToDevice));
+    }
+    for (int e = 0; e < s->E; ++e) {
+        if (!s->ln_on_device[e] && s->on_host[e]) {
+            INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln + (size_t)e * s->D, s->h_ln[e], sizeof(float) * s->D,
+                                       cudaMemcpyHostToDevice));
+            s->ln_on_device[e] = 1;
+        }
+    }
+    return INFMOE_OK;
+}
+
+int ensure_resident_planes(ExpertStore* s) {
+    for (int p = 0; p < 6; ++p)
+        if (!s->d_plane[p]) INFMOE_CUDA_TRY(cudaMalloc(&s->d_plane[p], sizeof(float) * s->matrix_elems() * s->E));
+    return INFMOE_OK;
+}
+
+// Uploads every expert that is on the host but not yet on the device (raw copy into the
+// head plane, then an in-place head/tail split).
+int upload_resident(ExpertStore* s, cudaStream_t stream) {
+    INFMOE_TRY(ensure_resident_planes(s));
+    const size_t n = s->matrix_elems();
+    for (int e = 0; e < s->E; ++e) {
+        if (s->on_device[e] || !s->on_host[e]) continue;
+        const float* src[3] = {s->h_wi0[e], s->h_wi1[e], s->h_wo[e]};
+        for (int m = 0; m < 3; ++m) {
+            float* hi = s->d_plane[2 * m] + (size_t)e * n;
+            float* lo = s->d_plane[2 * m + 1] + (size_t)e * n;
+            INFMOE_CUDA_TRY(cudaMemcpyAsync(hi, src[m], sizeof(float) * n, cudaMemcpyHostToDevice, stream));
+            INFMOE_TRY(launch_split(hi, hi, lo, n, stream));
+        }
+        s->on_device[e] = 1;
+    }
+    return INFMOE_OK;
+}
+
+int ensure_device(infmoe_layer* L) {
+    if (L->device_ready) return INFMOE_OK;
+    INFMOE_CUDA_TRY(cudaGetDevice(&L->device));
+    cudaDeviceProp prop;
+    INFMOE_CUDA_TRY(cudaGetDeviceProperties(&prop, L->device));
+    if (prop.major != 10) {
+        set_error("this library is built for sm_100a (B200); device %d is sm_%d%d", L->device, prop.major, prop.minor);
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    L->num_sms = prop.multiProcessorCount;
+    const size_t cbytes = sizeof(float) * (size_t)L->E * L->D;
+    INFMOE_CUDA_TRY(cudaMalloc(&L->d_centroids, cbytes));
+    INFMOE_CUDA_TRY(cudaMemcpy(L->d_centroids, L->centroids.data(), cbytes, cudaMemcpyHostToDevice));
+    if (!L->gating_ln.empty()) {
+        INFMOE_CUDA_TRY(cudaMalloc(&L->d_gating_ln, sizeof(float) * L->D));
+        INFMOE_CUDA_TRY(cudaMemcpy(L->d_gating_ln, L->gating_ln.data(), sizeof(float) * L->D, cudaMemcpyHostToDevice));
+    }
+    INFMOE_CUDA_TRY(cudaMalloc(&L->d_status, sizeof(int)));
+    INFMOE_CUDA_TRY(cudaMemset(L->d_status, 0, sizeof(int)));
+    INFMOE_CUDA_TRY(cudaHostAlloc(&L->h_status, sizeof(int), cudaHostAllocDefault));
+    *L->h_status = 0;
+    INFMOE_CUDA_TRY(cudaHostAlloc(&L->h_count, sizeof(int) * (L->E + 1), cudaHostAllocDefault));
+    INFMOE_CUDA_TRY(cudaHostAlloc(&L->h_slot_map, sizeof(int) * L->E, cudaHostAllocDefault));
+    const int ncopy = L->mc < 2 ? 1 : 2;
+    L->copy_streams.resize(ncopy);
+    for (auto& s : L->copy_streams) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    L->ev_ready.resize(L->mc);
+    L->ev_freed.resize(L->mc);
+    for (int i = 0; i < L->mc; ++i) {
+        INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&L->ev_ready[i], cudaEventDisableTiming));
+        INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&L->ev_freed[i], cudaEventDisableTiming));
+    }
+    INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming));
+    const char* path = getenv("INFMOE_FFN");
+    if (path && strcmp(path, "simt") == 0) L->ffn_path = 1;
+    L->device_ready = true;
+    return INFMOE_OK;
+}
+
+int resolve_residency(infmoe_layer* L) {
+    if (L->residency_resolved) return INFMOE_OK;
+    int mode = L->residency;
+    if (mode < 0) {
+        const char* env = getenv("INFMOE_RESIDENT");
+        if (env && *env) mode = atoi(env) ? 1 : 0;
+    }
+    ExpertStore* s = L->store.get();
+    bool any_host_only = false, any_device = false;
+    for (int e = 0; e < s->E; ++e) {
+        if (s->on_device[e]) any_device = true;
+        else if (s->on_host[e]) any_host_only = true;
+    }
+    if (L->identity) {
+        L->resident = true;
+    } else if (any_device) {
+        L->resident = true;  // weights were handed over on the device: nothing to stream from
+    } else if (mode < 0) {
+        size_t free_b = 0, total_b = 0;
+        INFMOE_CUDA_TRY(cudaMemGetInfo(&free_b, &total_b));
+        L->resident = s->resident_bytes() < free_b / 10 * 7;
+    } else {
+        L->resident = mode == 1;
+    }
+    (void)any_host_only;
+    L->residency_resolved = true;
+    return INFMOE_OK;
+}
+
+int status_to_rc(int status) {
+    if (status & STATUS_WAIT_TIMEOUT) {
+        set_error("a bounded device-side wait ran out inside the expert GEMM (status 0x%x)", status);
+        return INFMOE_ERR_DEVICE_TIMEOUT;
+    }
+    if (status & (STATUS_NO_EXPERT | STATUS_BAD_GATE)) {
+        set_error("routing selected no expert for at least one token (NaN in input, centroids or weights)");
+        return INFMOE_ERR_NAN;
+    }
+    if (status) {
+        set_error("device status 0x%x", status);
+        return INFMOE_ERR_CUDA;
+    }
+    return INFMOE_OK;
+}
+
+int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_offset, const int* d_slot_map,
+            int slots, float* const planes[6], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
+            float* g_lo, float* post, cudaStream_t stream) {
+    const bool umma = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);
+    if (umma)
+        return launch_ffn_umma(T, L->D, L->F, L->E, e_begin, e_end, d_offset, d_slot_map, slots, h_hi, h_lo, planes[0],
+                               planes[1], planes[2], planes[3], planes[4], planes[5], routed, g_hi, g_lo, post,
+                               L->d_status, L->num_sms, stream);
+    return launch_ffn_simt(T, L->D, L->F, e_begin, e_end, d_offset, d_slot_map, h_hi, h_lo, planes[0], planes[1],
+                           planes[2], planes[3], planes[4], planes[5], routed, g_hi, g_lo, post, stream);
+}
+
+void free_device_state(infmoe_layer* L) {
+    if (L->d_centroids) cudaFree(L->d_centroids);
+    if (L->d_gating_ln) cudaFree(L->d_gating_ln);
+    if (L->d_status) cudaFree(L->d_status);
+    if (L->h_status) cudaFreeHost(L->h_status);
+    if (L->h_count) cudaFreeHost(L->h_count);
+    if (L->h_slot_map) cudaFreeHost(L->h_slot_map);
+    for (auto s : L->copy_streams) cudaStreamDestroy(s);
+    for (auto e : L->ev_ready) cudaEventDestroy(e);
+    for (auto e : L->ev_freed) cudaEventDestroy(e);
+    if (L->ev_fork) cudaEventDestroy(L->ev_fork);
+    if (L->own_in) cudaFree(L->own_in);
+    if (L->own_out) cudaFree(L->own_out);
+    if (L->own_ws) cudaFree(L->own_ws);
+    if (L->own_stream) cudaStreamDestroy(L->own_stream);
+}
+
+std::shared_ptr<ExpertStore> make_store(int E, int D, int F) {
+    auto s = std::make_shared<ExpertStore>();
+    s->E = E;
+    s->D = D;
+    s->F = F;
+    s->h_ln.assign(E, nullptr);
+    s->h_wi0.assign(E, nullptr);
+    s->h_wi1.assign(E, nullptr);
+    s->h_wo.assign(E, nullptr);
+    s->on_host.assign(E, 0);
+    s->on_device.assign(E, 0);
+    s->ln_on_device.assign(E, 0);
+    return s;
+}
+
+int pinned_alloc(float** p, size_t elems) {
+    if (*p) return INFMOE_OK;
+    INFMOE_CUDA_TRY(cudaHostAlloc((void**)p, sizeof(float) * elems, cudaHostAllocDefault));
+    return INFMOE_OK;
+}
+
+constexpr uint32_t BLOB_MAGIC = 0x454F4D49u;  // "IMOE"
+constexpr uint32_t BLOB_VERSION = 1;
+
+}  // namespace
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+extern "C" {
+
+const char* infmoe_last_error(void) { return t_error; }
+
+int infmoe_layer_create(const infmoe_layer_config* cfg, infmoe_layer** out) {
+    if (!cfg || !out) {
+        set_error("layer_create: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    *out = nullptr;
+    if (cfg->expert_count <= 0 || cfg->embedding_size <= 0 || cfg->hidden_size <= 0) {
+        set_error("layer_create: expert_count, embedding_size and hidden_size must be positive");
+        return INFMOE_ERR_INVALID_ARGUMENT;  // plugin/MoELayerPluginCreator.cc:118-128
+    }
+    if (cfg->max_concurrency <= 0) {
+        set_error("layer_create: max_concurrency must be positive");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (!cfg->expert_centroids) {
+        set_error("layer_create: expert_centroids is required");
+        return INFMOE_ERR_INVALID_ARGUMENT;  // plugin/MoELayerPlugin.cc:75
+    }
+    Flags flags;
+    INFMOE_TRY(parse_flags(cfg->moe_variant, &flags));
+    if (flags.layernorm_before_score && !cfg->layernorm_weight) {
+        set_error("layer_create: layernorm_weight is required for moe_variant cpm_2");
+        return INFMOE_ERR_INVALID_ARGUMENT;  // plugin/MoELayerPlugin.cc:76-79
+    }
+    const char* type = cfg->expert_sublayer_type ? cfg->expert_sublayer_type : "T5_FF";
+    const bool identity = strcmp(type, "Identity") == 0;
+    if (!identity && strcmp(type, "T5_FF") != 0) {
+        set_error("unsupported sublayer type: %s", type);  // plugin/MoELayerPlugin.cc:37-39
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (cfg->expert_weight_file && *cfg->expert_weight_file) {
+        struct stat st;
+        if (stat(cfg->expert_weight_file, &st) != 0 || !S_ISREG(st.st_mode)) {
+            set_error("expert weight file %s is not a regular file", cfg->expert_weight_file);
+            return INFMOE_ERR_IO;  // plugin/MoELayerPluginCreator.cc:132-140
+        }
+    }
+    auto* L = new infmoe_layer();
+    L->E = cfg->expert_count;
+    L->D = cfg->embedding_size;
+    L->F = cfg->hidden_size;
+    L->mc = cfg->max_concurrency;
+    L->centroids.assign(cfg->expert_centroids, cfg->expert_centroids + (size_t)L->E * L->D);
+    if (cfg->layernorm_weight) L->gating_ln.assign(cfg->layernorm_weight, cfg->layernorm_weight + L->D);
+    L->weight_file = cfg->expert_weight_file ? cfg->expert_weight_file : "";
+    L->sublayer_type = type;
+    L->variant = cfg->moe_variant;
+    L->flags = flags;
+    L->identity = identity;
+    L->store = make_store(L->E, L->D, L->F);
+    L->launches_at_create = g_kernel_launches;
+    *out = L;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_clone(const infmoe_layer* src, infmoe_layer** out) {
+    if (!src || !out) {
+        set_error("layer_clone: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    auto* L = new infmoe_layer();
+    L->E = src->E;
+    L->D = src->D;
+    L->F = src->F;
+    L->mc = src->mc;
+    L->centroids = src->centroids;
+    L->gating_ln = src->gating_ln;
+    L->weight_file = src->weight_file;
+    L->sublayer_type = src->sublayer_type;
+    L->variant = src->variant;
+    L->flags = src->flags;
+    L->identity = src->identity;
+    L->store = src->store;  // shared, like the reference's sublayer
+    L->residency = src->residency;
+    L->initialized = src->initialized;
+    L->launches_at_create = g_kernel_launches;
+    *out = L;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_initialize(infmoe_layer* L) {
+    if (!L) {
+        set_error("layer_initialize: null layer");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (L->identity || L->weight_file.empty()) {
+        L->initialized = true;
+        return INFMOE_OK;
+    }
+    ExpertStore* s = L->store.get();
+    std::lock_guard<std::mutex> lock(s->mu);
+    bool all = true;
+    for (int e = 0; e < s->E; ++e) all = all && (s->on_host[e] || s->on_device[e]);
+    if (all) {  // already loaded through a clone (reference: mSavedWeights != nullptr, T5FFLayer.cc:145)
+        L->initialized = true;
+        return INFMOE_OK;
+    }
+    std::vector<int> seen((size_t)s->E, 0);
+    const int D = s->D, F = s->F, E = s->E;
+    auto alloc = [&](const std::string& name, const std::vector<int64_t>& shape, float** dst) -> int {
+        *dst = nullptr;
+        const size_t slash = name.find('/');
+        if (slash == std::string::npos) return INFMOE_OK;  // not an expert tensor: ignored like the reference
+        char* endp = nullptr;
+        const long e = strtol(name.c_str(), &endp, 10);
+        if (endp != name.c_str() + slash || e < 0 || e >= E) return INFMOE_OK;
+        const std::string key = name.substr(slash + 1);
+        size_t count = 1;
+        for (int64_t d : shape) count *= (size_t)d;
+        float** slot = nullptr;
+        size_t want = 0;
+        int bit = 0;
+        if (key == "layer_norm_weight") { slot = &s->h_ln[e]; want = (size_t)D; bit = 1; }
+        else if (key == "wi_0_weight") { slot = &s->h_wi0[e]; want = (size_t)D * F; bit = 2; }
+        else if (key == "wi_1_weight") { slot = &s->h_wi1[e]; want = (size_t)D * F; bit = 4; }
+        else if (key == "wo_weight") { slot = &s->h_wo[e]; want = (size_t)D * F; bit = 8; }
+        else return INFMOE_OK;
+        if (count != want) {  // reference: assert on num_bytes(), T5FFLayer.cc:61,68,75,82
+            set_error("%s: %s has %zu elements, expected %zu", L->weight_file.c_str(), name.c_str(), count, want);
+            return INFMOE_ERR_FORMAT;
+        }
+        INFMOE_TRY(pinned_alloc(slot, want));
+        *dst = *slot;
+        seen[e] |= bit;
+        return INFMOE_OK;
+    };
+    bool fortran = false;
+    INFMOE_TRY(npz_read(L->weight_file.c_str(), alloc, &fortran));
+    s->fortran_warning = fortran;
+    for (int e = 0; e < E; ++e) {
+        if (seen[e] != 15) {
+            set_error("%s: expert %d is missing tensors (mask 0x%x of 0xf)", L->weight_file.c_str(), e, seen[e]);
+            return INFMOE_ERR_FORMAT;
+        }
+        s->on_host[e] = 1;
+        s->on_device[e] = 0;
+        s->ln_on_device[e] = 0;
+    }
+    L->initialized = true;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const float* wi0, const float* wi1,
+                            const float* wo, int on_device) {
+    if (!L || !ln_w || !wi0 || !wi1 || !wo || e < 0 || e >= L->E) {
+        set_error("layer_set_expert: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    ExpertStore* s = L->store.get();
+    std::lock_guard<std::mutex> lock(s->mu);
+    const size_t n = s->matrix_elems();
+    if (on_device) {
+        if (!s->d_ln) INFMOE_TRY(ensure_store_device_ln(s));
+        INFMOE_TRY(ensure_resident_planes(s));
+        INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln + (size_t)e * s->D, ln_w, sizeof(float) * s->D, cudaMemcpyDeviceToDevice));
+        s->ln_on_device[e] = 1;
+        const float* src[3] = {wi0, wi1, wo};
+        for (int m = 0; m < 3; ++m)
+            INFMOE_TRY(launch_split(src[m], s->d_plane[2 * m] + (size_t)e * n, s->d_plane[2 * m + 1] + (size_t)e * n, n,
+                                    0));
+        INFMOE_CUDA_TRY(cudaStreamSynchronize(0));
+        s->on_device[e] = 1;
+    } else {
+        INFMOE_TRY(pinned_alloc(&s->h_ln[e], (size_t)s->D));
+        INFMOE_TRY(pinned_alloc(&s->h_wi0[e], n));
+        INFMOE_TRY(pinned_alloc(&s->h_wi1[e], n));
+        INFMOE_TRY(pinned_alloc(&s->h_wo[e], n));
+        memcpy(s->h_ln[e], ln_w, sizeof(float) * s->D);
+        memcpy(s->h_wi0[e], wi0, sizeof(float) * n);
+        memcpy(s->h_wi1[e], wi1, sizeof(float) * n);
+        memcpy(s->h_wo[e], wo, sizeof(float) * n);
+        s->on_host[e] = 1;
+        s->on_device[e] = 0;
+        s->ln_on_device[e] = 0;
+    }
+    L->initialized = true;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_set_residency(infmoe_layer* L, int mode) {
+    if (!L || mode < -1 || mode > 1) {
+        set_error("layer_set_residency: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    L->residency = mode;
+    L->residency_resolved = false;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes) {
+    if (!L || !bytes || T < 0) {
+        set_error("layer_workspace_bytes: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    // Sized for the streamed case so that the answer does not depend on a decision taken later.
+    *bytes = ws_layout(L, T, true).total + ALIGN;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
+                         void* stream_v) {
+    if (!L || T < 0 || (T > 0 && (!d_in || !d_out || !d_ws))) {
+        set_error("layer_enqueue: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    if (d_in == d_out) {
+        set_error("layer_enqueue: input and output must not alias");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T > 0x7fffffffLL / (L->D > L->F ? L->D : L->F)) {
+        set_error("layer_enqueue: token_num %lld is too large for 32-bit row offsets", (long long)T);
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    ExpertStore* s = L->store.get();
+    INFMOE_TRY(ensure_device(L));
+    if (!L->identity) {
+        std::lock_guard<std::mutex> lock(s->mu);
+        for (int e = 0; e < s->E; ++e) {
+            if (!s->on_host[e] && !s->on_device[e]) {
+                set_error("layer_enqueue: expert %d has no weights (call infmoe_layer_initialize first)", e);
+                return INFMOE_ERR_STATE;
+            }
+        }
+        INFMOE_TRY(ensure_store_device_ln(s));
+        INFMOE_TRY(resolve_residency(L));
+        if (L->resident) INFMOE_TRY(upload_resident(s, stream));
+    } else {
+        L->resident = true;
+    }
+    const bool streamed = !L->resident;
+    const WsLayout w = ws_layout(L, T, streamed);
+    char* base = (char*)(((uintptr_t)d_ws + ALIGN - 1) / ALIGN * ALIGN);
+    if ((size_t)(base - (char*)d_ws) + w.total > ws_bytes) {
+        set_error("layer_enqueue: workspace of %zu bytes is too small, %zu needed", ws_bytes, w.total + ALIGN);
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    int* gate = (int*)(base + w.gate);
+    int* pos = (int*)(base + w.pos);
+    int* count = (int*)(base + w.count);
+    int* offset = (int*)(base + w.offset);
+    int* slot_map = (int*)(base + w.slot_map);
+    float* score = (float*)(base + w.score);
+    float* rscore = (float*)(base + w.rscore);
+    float* routed = (float*)(base + w.routed);
+    float* post = (float*)(base + w.post);
+    float* h_hi = (float*)(base + w.h_hi);
+    float* h_lo = (float*)(base + w.h_lo);
+    float* g_hi = (float*)(base + w.g_hi);
+    float* g_lo = (float*)(base + w.g_lo);
+    L->last_gate = gate;
+    L->last_score = score;
+    L->last_pos = pos;
+    L->last_count = count;
+    L->last_offset = offset;
+
+    // 1. routing (plugin/MoELayerPlugin.cc:312-345)
+    INFMOE_TRY(launch_route(d_in, L->d_centroids, L->flags.layernorm_before_score ? L->d_gating_ln : nullptr, T, L->D,
+                            L->E, gate, score, L->d_status, stream));
+    // 2. dispatch metadata (:350-352)
+    INFMOE_TRY(launch_dispatch(gate, T, L->E, pos, count, offset, L->d_status, stream));
+    if (L->identity) {
+        // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
+        INFMOE_TRY(launch_scatter(T, L->D, d_in, score, pos, routed, rscore, stream));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(post, routed, sizeof(float) * (size_t)T * L->D, cudaMemcpyDeviceToDevice, stream));
+    } else {
+        // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
+        INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate, s->d_ln, routed, rscore, h_hi, h_lo, stream));
+        // 4. experts (:360-402)
+        if (!streamed) {
+            INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, nullptr, L->E, s->d_plane, h_hi, h_lo, routed, g_hi, g_lo, post,
+                               stream));
+        } else {
+            const size_t n = s->matrix_elems();
+            float* planes[6];
+            for (int p = 0; p < 6; ++p) planes[p] = (float*)(base + w.slots) + (size_t)p * L->mc * n;
+            // the one host synchronisation of the streamed path: which experts have rows?
+            INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_count, count, sizeof(int) * L->E, cudaMemcpyDeviceToHost, stream));
+            INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+            INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+            if (*L->h_status) {
+                const int st = *L->h_status;
+                cudaMemsetAsync(L->d_status, 0, sizeof(int), stream);
+                *L->h_status = 0;
+                return status_to_rc(st);
+            }
+            std::vector<int> active;
+            for (int e = 0; e < L->E; ++e) {
+                L->h_slot_map[e] = 0;
+                if (L->h_count[e] > 0) {
+                    L->h_slot_map[e] = (int)(active.size() % (size_t)L->mc);
+                    active.push_back(e);
+                }
+            }
+            INFMOE_CUDA_TRY(cudaMemcpyAsync(slot_map, L->h_slot_map, sizeof(int) * L->E, cudaMemcpyHostToDevice, stream));
+            // copy streams may touch the slots only after everything queued so far on `stream`
+            INFMOE_CUDA_TRY(cudaEventRecord(L->ev_fork, stream));
+            for (auto cs : L->copy_streams) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_fork, 0));
+            for (size_t j = 0; j < active.size(); ++j) {
+                const int e = active[j];
+                const int slot = (int)(j % (size_t)L->mc);
+                cudaStream_t cs = L->copy_streams[j % L->copy_streams.size()];
+                // the slot is free once the expert that used it (j - mc) has run
+                if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
+                const float* src[3] = {s->h_wi0[e], s->h_wi1[e], s->h_wo[e]};
+                for (int m = 0; m < 3; ++m) {
+                    float* hi = planes[2 * m] + (size_t)slot * n;
+                    float* lo = planes[2 * m + 1] + (size_t)slot * n;
+                    INFMOE_CUDA_TRY(cudaMemcpyAsync(hi, src[m], sizeof(float) * n, cudaMemcpyHostToDevice, cs));
+                    INFMOE_TRY(launch_split(hi, hi, lo, n, cs));
+                }
+                INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
+                INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
+                INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, L->mc, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
+                                   stream));
+                INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[slot], stream));
+            }
+        }
+    }
+    // 5. combine (:407-412; the gather reads the expert output)
+    if (L->flags.base_layer_mix)
+        INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, d_out, stream));
+    else
+        INFMOE_TRY(launch_gather(T, L->D, post, pos, d_out, stream));
+    return INFMOE_OK;
+}
+
+int infmoe_layer_sync_status(infmoe_layer* L, void* stream_v) {
+    if (!L) {
+        set_error("layer_sync_status: null layer");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (!L->device_ready) return INFMOE_OK;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(L->d_status, 0, sizeof(int), stream));
+    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+    const int st = *L->h_status;
+    *L->h_status = 0;
+    return status_to_rc(st);
+}
+
+int infmoe_layer_forward_host(infmoe_layer* L, const float* h_in, float* h_out, int64_t T) {
+    if (!L || T < 0 || (T > 0 && (!h_in || !h_out))) {
+        set_error("layer_forward_host: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    if (!L->own_stream) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking));
+    const size_t io = sizeof(float) * (size_t)T * L->D;
+    if (io > L->own_io_bytes) {
+        if (L->own_in) cudaFree(L->own_in);
+        if (L->own_out) cudaFree(L->own_out);
+        L->own_in = L->own_out = nullptr;
+        L->own_io_bytes = 0;
+        INFMOE_CUDA_TRY(cudaMalloc(&L->own_in, io));
+        INFMOE_CUDA_TRY(cudaMalloc(&L->own_out, io));
+        L->own_io_bytes = io;
+    }
+    size_t need = 0;
+    INFMOE_TRY(infmoe_layer_workspace_bytes(L, T, &need));
+    if (need > L->own_ws_bytes) {
+        if (L->own_ws) cudaFree(L->own_ws);
+        L->own_ws = nullptr;
+        L->own_ws_bytes = 0;
+        INFMOE_CUDA_TRY(cudaMalloc(&L->own_ws, need));
+        L->own_ws_bytes = need;
+    }
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(L->own_in, h_in, io, cudaMemcpyHostToDevice, L->own_stream));
+    INFMOE_TRY(infmoe_layer_enqueue(L, L->own_in, L->own_out, L->own_ws, L->own_ws_bytes, T, L->own_stream));
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, L->own_out, io, cudaMemcpyDeviceToHost, L->own_stream));
+    return infmoe_layer_sync_status(L, L->own_stream);
+}
+
+int infmoe_layer_last_routing(const infmoe_layer* L, const int32_t** gate, const float** score, const int32_t** pos,
+                              const int32_t** count, const int32_t** offset) {
+    if (!L) {
+        set_error("layer_last_routing: null layer");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (!L->last_gate) {
+        set_error("layer_last_routing: no enqueue has run yet");
+        return INFMOE_ERR_STATE;
+    }
+    if (gate) *gate = L->last_gate;
+    if (score) *score = L->last_score;
+    if (pos) *pos = L->last_pos;
+    if (count) *count = L->last_count;
+    if (offset) *offset = L->last_offset;
+    return INFMOE_OK;
+}
+
+int64_t infmoe_layer_kernel_launches(const infmoe_layer* L) {
+    return L ? (int64_t)(g_kernel_launches - L->launches_at_create) : (int64_t)g_kernel_launches;
+}
+
+int infmoe_layer_destroy(infmoe_layer* L) {
+    if (!L) return INFMOE_OK;
+    if (L->device_ready || L->own_stream) {
+        cudaDeviceSynchronize();
+        free_device_state(L);
+    }
+    delete L;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_serialization_size(const infmoe_layer* L, size_t* bytes) {
+    if (!L || !bytes) {
+        set_error("layer_serialization_size: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    size_t n = 8 + 6 * 4 + 4;                                              // magic, version, 6 ints, flags
+    n += L->weight_file.size() + 1 + L->sublayer_type.size() + 1;          // two NUL-terminated strings
+    n = (n + 7) / 8 * 8;                                                   // floats start 8-byte aligned
+    n += sizeof(float) * L->centroids.size() + sizeof(float) * L->gating_ln.size();
+    *bytes = n;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_serialize(const infmoe_layer* L, void* buffer, size_t bytes) {
+    size_t need = 0;
+    INFMOE_TRY(infmoe_layer_serialization_size(L, &need));
+    if (!buffer || bytes < need) {
+        set_error("layer_serialize: buffer of %zu bytes is too small, %zu needed", bytes, need);
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    uint8_t* p = (uint8_t*)buffer;
+    memset(p, 0, need);
+    auto put32 = [&](uint32_t v) {
+        memcpy(p, &v, 4);
+        p += 4;
+    };
+    put32(BLOB_MAGIC);
+    put32(BLOB_VERSION);
+    put32((uint32_t)L->E);                        // field order of plugin/MoELayerPlugin.cc:429-436
+    put32((uint32_t)L->D);
+    put32((uint32_t)L->F);
+    put32((uint32_t)L->mc);
+    put32((uint32_t)L->weight_file.size());
+    put32((uint32_t)L->sublayer_type.size());
+    *p++ = L->flags.layernorm_before_score ? 1 : 0;  // MoEFlags, plugin/MoELayerPlugin.h:36-42
+    *p++ = L->flags.base_layer_mix ? 1 : 0;
+    p += 2;
+    memcpy(p, L->weight_file.c_str(), L->weight_file.size() + 1);
+    p += L->weight_file.size() + 1;
+    memcpy(p, L->sublayer_type.c_str(), L->sublayer_type.size() + 1);
+    p += L->sublayer_type.size() + 1;
+    p = (uint8_t*)buffer + ((size_t)(p - (uint8_t*)buffer) + 7) / 8 * 8;
+    memcpy(p, L->centroids.data(), sizeof(float) * L->centroids.size());
+    p += sizeof(float) * L->centroids.size();
+    memcpy(p, L->gating_ln.data(), sizeof(float) * L->gating_ln.size());
+    return INFMOE_OK;
+}
+
+int infmoe_layer_deserialize(const void* buffer, size_t bytes, infmoe_layer** out) {
+    if (!buffer || !out || bytes < 36) {
+        set_error("layer_deserialize: blob too short");
+        return INFMOE_ERR_FORMAT;
+    }
+    const uint8_t* p = (const uint8_t*)buffer;
+    const uint8_t* end = p + bytes;
+    uint32_t v[8];
+    memcpy(v, p, 32);
+    p += 32;
+    if (v[0] != BLOB_MAGIC || v[1] != BLOB_VERSION) {
+        set_error("layer_deserialize: bad magic or version");
+        return INFMOE_ERR_FORMAT;
+    }
+    const int E = (int)v[2], D = (int)v[3], F = (int)v[4], mc = (int)v[5];
+    const size_t flen = v[6], tlen = v[7];
+    const bool ln = p[0] != 0, mix = p[1] != 0;
+    p += 4;
+    if (E <= 0 || D <= 0 || F <= 0 || mc <= 0 || (size_t)(end - p) < flen + tlen + 2) {
+        set_error("layer_deserialize: corrupt header");
+        return INFMOE_ERR_FORMAT;
+    }
+    if (p[flen] != 0 || p[flen + 1 + tlen] != 0) {
+        set_error("layer_deserialize: strings are not terminated");
+        return INFMOE_ERR_FORMAT;
+    }
+    const std::string file((const char*)p, flen), type((const char*)p + flen + 1, tlen);
+    p += flen + tlen + 2;
+    p = (const uint8_t*)buffer + ((size_t)(p - (const uint8_t*)buffer) + 7) / 8 * 8;
+    const size_t nfloat = (size_t)E * D + (ln ? (size_t)D : 0);
+    if (p > end || (size_t)(end - p) < nfloat * sizeof(float)) {
+        set_error("layer_deserialize: blob of %zu bytes is truncated", bytes);
+        return INFMOE_ERR_FORMAT;
+    }
+    std::vector<float> cent((size_t)E * D), gl(ln ? (size_t)D : 0);
+    memcpy(cent.data(), p, sizeof(float) * cent.size());
+    if (ln) memcpy(gl.data(), p + sizeof(float) * cent.size(), sizeof(float) * gl.size());
+    infmoe_layer_config cfg{};
+    cfg.expert_count = E;
+    cfg.embedding_size = D;
+    cfg.hidden_size = F;
+    cfg.max_concurrency = mc;
+    cfg.expert_centroids = cent.data();
+    cfg.layernorm_weight = ln ? gl.data() : nullptr;
+    cfg.expert_weight_file = file.c_str();
+    cfg.expert_sublayer_type = type.c_str();
+    cfg.moe_variant = mix ? "base_layer" : (ln ? "cpm_2" : "default");
+    return infmoe_layer_create(&cfg, out);
+}
+
+int infmoe_weight_file_check(const char* path, int32_t E, int32_t D, int32_t F, double* h_sums) {
+    if (!path || E <= 0 || D <= 0 || F <= 0) {
+        set_error("weight_file_check: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    std::vector<int> seen((size_t)E, 0);
+    std::vector<float> buf;
+    struct Pending { int e, k; size_t n; } pend{-1, 0, 0};
+    auto flush = [&]() {
+        if (pend.e >= 0 && h_sums) {
+            double acc = 0;
+            for (size_t i = 0; i < pend.n; ++i) acc += buf[i];
+            h_sums[(size_t)pend.e * 4 + pend.k] = acc;
+        }
+        pend.e = -1;
+    };
+    auto alloc = [&](const std::string& name, const std::vector<int64_t>& shape, float** dst) -> int {
+        flush();
+        *dst = nullptr;
+        const size_t slash = name.find('/');
+        if (slash == std::string::npos) return INFMOE_OK;
+        char* endp = nullptr;
+        const long e = strtol(name.c_str(), &endp, 10);
+        if (endp != name.c_str() + slash || e < 0 || e >= E) return INFMOE_OK;
+        const std::string key = name.substr(slash + 1);
+        size_t count = 1;
+        for (int64_t d : shape) count *= (size_t)d;
+        int k = -1;
+        size_t want = (size_t)D * F;
+        if (key == "layer_norm_weight") { k = 0; want = (size_t)D; }
+        else if (key == "wi_0_weight") k = 1;
+        else if (key == "wi_1_weight") k = 2;
+        else if (key == "wo_weight") k = 3;
+        else return INFMOE_OK;
+        if (count != want) {
+            set_error("%s: %s has %zu elements, expected %zu", path, name.c_str(), count, want);
+            return INFMOE_ERR_FORMAT;
+        }
+        buf.resize(want);
+        *dst = buf.data();
+        seen[e] |= 1 << k;
+        pend = {(int)e, k, want};
+        return INFMOE_OK;
+    };
+    bool fortran = false;
+    INFMOE_TRY(npz_read(path, alloc, &fortran));
+    flush();
+    for (int e = 0; e < E; ++e) {
+        if (seen[e] != 15) {
+            set_error("%s: expert %d is missing tensors (mask 0x%x of 0xf)", path, e, seen[e]);
+            return INFMOE_ERR_FORMAT;
+        }
+    }
+    return INFMOE_OK;
+}
+
+int infmoe_layer_get_config(const infmoe_layer* L, infmoe_layer_config* out) {
+    if (!L || !out) {
+        set_error("layer_get_config: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    out->expert_count = L->E;
+    out->embedding_size = L->D;
+    out->hidden_size = L->F;
+    out->max_concurrency = L->mc;
+    out->expert_centroids = L->centroids.data();
+    out->layernorm_weight = L->gating_ln.empty() ? nullptr : L->gating_ln.data();
+    out->expert_weight_file = L->weight_file.c_str();
+    out->expert_sublayer_type = L->sublayer_type.c_str();
+    out->moe_variant = L->variant.c_str();
+    return INFMOE_OK;
+}
+
+// ---- stage entry points -------------------------------------------------------------------------
+
+int infmoe_route(const float* x, const float* centroids, const float* ln_w, int64_t T, int32_t D, int32_t E,
+                 int32_t* gate, float* score, int32_t* status, void* stream) {
+    return launch_route(x, centroids, ln_w, T, D, E, gate, score, status, (cudaStream_t)stream);
+}
+
+int infmoe_expert_select(int64_t T, int32_t E, const float* aff, int32_t* gate, float* weight, int32_t* status,
+                         void* stream) {
+    return launch_select_top1(T, E, aff, gate, weight, status, (cudaStream_t)stream);
+}
+
+int infmoe_expert_count(int64_t T, int32_t E, const int32_t* gate, int32_t* pos, int32_t* count, int32_t* offset,
+                        int32_t* status, void* stream) {
+    return launch_dispatch(gate, T, E, pos, count, offset, status, (cudaStream_t)stream);
+}
+
+int infmoe_expert_scatter(int64_t T, int32_t D, const float* in, const float* coeff, const int32_t* pos,
+                          float* routed, float* routed_coeff, void* stream) {
+    return launch_scatter(T, D, in, coeff, pos, routed, routed_coeff, (cudaStream_t)stream);
+}
+
+int infmoe_expert_gather(int64_t T, int32_t D, const float* routed, const int32_t* pos, float* out, void* stream) {
+    return launch_gather(T, D, routed, pos, out, (cudaStream_t)stream);
+}
+
+int infmoe_expert_mix_gather(int64_t T, int32_t D, const int32_t* pos, const float* routed, const float* post,
+                             const float* coeff, float* out, void* stream) {
+    return launch_mix_gather(T, D, pos, routed, post, coeff, out, (cudaStream_t)stream);
+}
+
+int infmoe_layernorm(float* out, const float* in, int64_t rows, int32_t cols, const float* gamma, void* stream) {
+    return launch_layernorm(out, in, rows, cols, gamma, (cudaStream_t)stream);
+}
+
+int infmoe_gelu_dot(const float* a, float* b, size_t len, void* stream) {
+    return launch_gelu_dot(a, b, len, (cudaStream_t)stream);
+}
+
+int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* bytes) {
+    if (!bytes || rows < 0 || D <= 0 || F <= 0) {
+        set_error("t5ff_workspace_bytes: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
+    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + 6 * align_up(4 * d * f) + 2 * ALIGN + ALIGN;
+    return INFMOE_OK;
+}
+
+int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const float* wi0, const float* wi1,
+                    const float* wo, const float* x, float* y, void* ws, size_t ws_bytes, void* stream_v) {
+    if (rows < 0 || D <= 0 || F <= 0 || !ln_w || !wi0 || !wi1 || !wo || (rows > 0 && (!x || !y || !ws))) {
+        set_error("t5ff_run: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0) return INFMOE_OK;
+    size_t need = 0;
+    INFMOE_TRY(infmoe_t5ff_workspace_bytes(rows, D, F, &need));
+    if (ws_bytes < need) {
+        set_error("t5ff_run: workspace of %zu bytes is too small, %zu needed", ws_bytes, need);
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
+    char* p = (char*)(((uintptr_t)ws + ALIGN - 1) / ALIGN * ALIGN);
+    auto take = [&](size_t bytes) {
+        char* at = p;
+        p += align_up(bytes);
+        return at;
+    };
+    float* h_hi = (float*)take(4 * r * d);
+    float* h_lo = (float*)take(4 * r * d);
+    float* g_hi = (float*)take(4 * r * f);
+    float* g_lo = (float*)take(4 * r * f);
+    float* planes[6];
+    for (auto& pl : planes) pl = (float*)take(4 * d * f);
+    int* offset = (int*)take(8);
+    int* status = (int*)take(4);
+    const int h_offset[2] = {0, (int)rows};
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
+    const float* src[3] = {wi0, wi1, wo};
+    for (int m = 0; m < 3; ++m) INFMOE_TRY(launch_split(src[m], planes[2 * m], planes[2 * m + 1], d * f, stream));
+    int dev = 0, sms = 0;
+    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
+    INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const char* path = getenv("INFMOE_FFN");
+    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
+    if (simt)
+        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], planes[2],
+                                   planes[3], planes[4], planes[5], x, g_hi, g_lo, y, stream));
+    else
+        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], planes[2],
+                                   planes[3], planes[4], planes[5], x, g_hi, g_lo, y, status, sms, stream));
+    int h_status = 0;
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+    return status_to_rc(h_status);
+}
+
+}  // extern "C"

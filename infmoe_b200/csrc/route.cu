@@ -1,0 +1,191 @@
+// Fused routing for the MoE layer: optional pre-gating LayerNorm, centroid
+// scores and top-1 selection in one kernel.
+//
+// Replaces three reference launches and two host synchronisations:
+//   layernorm_gpu        plugin/MoELayerPlugin.cc:324  (kernel plugin/cuda/ops/layernorm.cu:136-174)
+//   cublasSgemm_v2       plugin/MoELayerPlugin.cc:334-336  (aff = Xs * C^T)
+//   moe_expert_select    plugin/cuda/moe.cu:147-159     (strict '>' scan, first maximum wins)
+//
+// Layout: X [T][D], centroids [E][D], both row-major FP32.  A warp owns TPW
+// tokens at once and, for a group of EG experts at a time, keeps TPW*EG
+// per-lane partial sums in registers; every centroid fragment loaded is used
+// for TPW tokens.  The per-(token, expert) summation order does not depend on
+// the blocking, so the result is the canonical order of common.cuh bit for bit.
+// All arithmetic is explicit round-to-nearest FP32 (no tensor cores).
+#include "common.cuh"
+
+namespace infmoe {
+
+namespace {
+
+constexpr int ROUTE_WARPS = 8;
+
+template <int TPW, int EG>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
+             long long T, int D, int E, int vec, int* __restrict__ gate, float* __restrict__ score,
+             int* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const long long t0 = ((long long)blockIdx.x * ROUTE_WARPS + warp) * TPW;
+    if (t0 >= T) return;
+
+    const float* rows[TPW];
+    float mean[TPW], rstd[TPW];
+    bool live[TPW];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+        live[i] = t0 + i < T;
+        rows[i] = X + (live[i] ? (t0 + i) : t0) * (long long)D;  // dead slots alias the first row
+        mean[i] = 0.f;
+        rstd[i] = 1.f;
+    }
+    const bool use_ln = gamma != nullptr;
+    if (use_ln) {
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) warp_row_stats(rows[i], D, vec != 0, mean[i], rstd[i]);
+    }
+
+    float best[TPW];
+    int best_e[TPW];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+        best[i] = -FLT_MAX;   // reference plugin/cuda/moe.cu:26-27
+        best_e[i] = -1;
+    }
+
+    for (int e0 = 0; e0 < E; e0 += EG) {
+        float acc[TPW][EG];
+#pragma unroll
+        for (int i = 0; i < TPW; ++i)
+#pragma unroll
+            for (int j = 0; j < EG; ++j) acc[i][j] = 0.f;
+
+        for (int base = 4 * lane; base < D; base += 128) {
+            float xs[TPW][4];
+            float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (use_ln) g4 = load_row4(gamma, base, D, vec != 0);
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+                const float4 v = load_row4(rows[i], base, D, vec != 0);
+                if (use_ln) {
+                    xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g4.x);
+                    xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g4.y);
+                    xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g4.z);
+                    xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g4.w);
+                } else {
+                    xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
+                }
+            }
+            const int nvalid = min(4, D - base);
+#pragma unroll
+            for (int j = 0; j < EG; ++j) {
+                if (e0 + j < E) {
+                    const float4 c = load_row4(C + (long long)(e0 + j) * D, base, D, vec != 0);
+                    const float cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (k < nvalid) {
+#pragma unroll
+                            for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < EG; ++j) {
+            if (e0 + j < E) {
+#pragma unroll
+                for (int i = 0; i < TPW; ++i) {
+                    const float s = warp_xor_sum(acc[i][j]);
+                    if (s > best[i]) {  // strict '>': the first maximum wins (plugin/cuda/moe.cu:62-67)
+                        best[i] = s;
+                        best_e[i] = e0 + j;
+                    }
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) {
+            if (!live[i]) continue;
+            gate[t0 + i] = best_e[i];
+            if (score) score[t0 + i] = best[i];
+            if (best_e[i] < 0 && status) atomicOr(status, STATUS_NO_EXPERT);
+        }
+    }
+}
+
+// Top-1 over a materialised score matrix (one warp per token; lanes scan
+// strided expert indices and the lowest index wins ties, which equals the
+// reference's sequential strict '>' scan).
+__global__ void select_top1_kernel(long long T, int E, const float* __restrict__ aff, int* __restrict__ gate,
+                                   float* __restrict__ weight, int* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (t >= T) return;
+    const float* row = aff + t * E;
+    float best = -FLT_MAX;
+    int best_e = -1;
+    for (int e = lane; e < E; e += 32) {
+        const float s = row[e];
+        if (s > best) {
+            best = s;
+            best_e = e;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+        const bool take = (oe >= 0) && (best_e < 0 || ob > best || (ob == best && oe < best_e));
+        if (take) {
+            best = ob;
+            best_e = oe;
+        }
+    }
+    if (lane == 0) {
+        gate[t] = best_e;
+        if (weight) weight[t] = best;
+        if (best_e < 0 && status) atomicOr(status, STATUS_NO_EXPERT);
+    }
+}
+
+}  // namespace
+
+int launch_route(const float* X, const float* C, const float* gamma, long long T, int D, int E, int* gate,
+                 float* score, int* status, cudaStream_t stream) {
+    if (T < 0 || D <= 0 || E <= 0 || !X || !C || !gate) {
+        set_error("route: bad argument (T=%lld D=%d E=%d)", T, D, E);
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    const bool vec = (D % 4 == 0) && (((uintptr_t)X | (uintptr_t)C | (uintptr_t)gamma) % 16 == 0);
+    constexpr int TPW = 4, EG = 16;
+    const long long tokens_per_cta = (long long)ROUTE_WARPS * TPW;
+    const long long grid = (T + tokens_per_cta - 1) / tokens_per_cta;
+    route_kernel<TPW, EG><<<(unsigned)grid, ROUTE_WARPS * 32, 0, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate,
+                                                                          score, status);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_select_top1(long long T, int E, const float* aff, int* gate, float* weight, int* status,
+                       cudaStream_t stream) {
+    if (T < 0 || E <= 0 || !aff || !gate) {
+        set_error("expert_select: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    const int threads = 256;
+    const long long grid = (T * 32 + threads - 1) / threads;
+    select_top1_kernel<<<(unsigned)grid, threads, 0, stream>>>(T, E, aff, gate, weight, status);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+}  // namespace infmoe

@@ -1,0 +1,297 @@
+// Row-wise kernels of the MoE layer: scatter into expert-contiguous order,
+// gather / mix back to token order, LayerNorm, gelu-dot and the TF32 head/tail
+// split that feeds the tensor-core GEMMs.  All of them are pure HBM streaming:
+// one warp per row, 128-bit loads and stores, rows of one warp contiguous.
+//
+// Reference counterparts (all scalar 4-byte copies, one CTA of 256 threads per row):
+//   batch_scatter_feature_and_weight_kernel  plugin/cuda/moe.cu:98-113
+//   batch_gather_kernel                      plugin/cuda/moe.cu:89-96
+//   fused_batch_mix_and_gather_kernel        plugin/cuda/moe.cu:115-127
+//   cuApplyLayerNorm                         plugin/cuda/ops/layernorm.cu:136-174
+//   gelu_dot functor via thrust::transform   plugin/cuda/ops/gelu.cu:6-25
+#include "common.cuh"
+
+namespace infmoe {
+
+namespace {
+
+constexpr int ROW_WARPS = 8;
+
+__device__ __forceinline__ void copy_row(const float* __restrict__ src, float* __restrict__ dst, int D, bool vec,
+                                         int lane) {
+    if (vec) {
+        const float4* s4 = reinterpret_cast<const float4*>(src);
+        float4* d4 = reinterpret_cast<float4*>(dst);
+        for (int i = lane; i < D / 4; i += 32) d4[i] = s4[i];
+    } else {
+        for (int i = lane; i < D; i += 32) dst[i] = src[i];
+    }
+}
+
+// routed[j,:] = X[pos[j],:]; rcoeff[j] = coeff[pos[j]]
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+scatter_kernel(long long T, int D, int vec, const float* __restrict__ X, const float* __restrict__ coeff,
+               const int* __restrict__ pos, float* __restrict__ routed, float* __restrict__ rcoeff) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= T) return;
+    const int p = pos[j];
+    copy_row(X + (long long)p * D, routed + j * D, D, vec != 0, lane);
+    if (lane == 0 && coeff && rcoeff) rcoeff[j] = coeff[p];
+}
+
+// The layer's fused scatter: one read of X[pos[j],:] produces the routed row,
+// its per-expert LayerNorm h = LN(x; gamma_e) (T5FFLayer.cc:99-103) already
+// split into TF32 head and tail planes for the tensor-core GEMM, and the
+// routed score.  gamma is [E][D]; the expert of row j is gate[pos[j]].
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X, const float* __restrict__ score,
+                        const int* __restrict__ pos, const int* __restrict__ gate,
+                        const float* __restrict__ gamma_all, float* __restrict__ routed,
+                        float* __restrict__ rscore, float* __restrict__ h_hi, float* __restrict__ h_lo) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= T) return;
+    const int p = pos[j];
+    const int e = gate[p];
+    const float* src = X + (long long)p * D;
+    const float* gamma = gamma_all + (long long)e * D;
+    float mean, rstd;
+    warp_row_stats(src, D, vec != 0, mean, rstd);
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 v = load_row4(src, base, D, vec != 0);
+        const float4 g = load_row4(gamma, base, D, vec != 0);
+        float4 hi, lo;
+        split_tf32(ln_apply(v.x, mean, rstd, g.x), hi.x, lo.x);
+        split_tf32(ln_apply(v.y, mean, rstd, g.y), hi.y, lo.y);
+        split_tf32(ln_apply(v.z, mean, rstd, g.z), hi.z, lo.z);
+        split_tf32(ln_apply(v.w, mean, rstd, g.w), hi.w, lo.w);
+        const long long o = j * D + base;
+        if (vec) {
+            if (routed) *reinterpret_cast<float4*>(routed + o) = v;
+            *reinterpret_cast<float4*>(h_hi + o) = hi;
+            *reinterpret_cast<float4*>(h_lo + o) = lo;
+        } else {
+            const float vv[4] = {v.x, v.y, v.z, v.w}, hh[4] = {hi.x, hi.y, hi.z, hi.w},
+                        ll[4] = {lo.x, lo.y, lo.z, lo.w};
+            for (int k = 0; k < 4 && base + k < D; ++k) {
+                if (routed) routed[o + k] = vv[k];
+                h_hi[o + k] = hh[k];
+                h_lo[o + k] = ll[k];
+            }
+        }
+    }
+    if (lane == 0 && rscore && score) rscore[j] = score[p];
+}
+
+// out[pos[j],:] = in[j,:]
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+gather_kernel(long long T, int D, int vec, const float* __restrict__ in, const int* __restrict__ pos,
+              float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= T) return;
+    copy_row(in + j * D, out + (long long)pos[j] * D, D, vec != 0, lane);
+}
+
+// alpha = 1 / (1 + exp(-coeff[j])); out[pos[j],:] = alpha * post[j,:] + (1 - alpha) * routed[j,:]
+// (sigmoid: plugin/cuda/common.cuh:24-27)
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+mix_gather_kernel(long long T, int D, int vec, const int* __restrict__ pos, const float* __restrict__ routed,
+                  const float* __restrict__ post, const float* __restrict__ coeff, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= T) return;
+    const float alpha = 1.0f / (1.0f + expf(-coeff[j]));
+    const float beta = 1.0f - alpha;
+    const float* a = post + j * D;
+    const float* b = routed + j * D;
+    float* o = out + (long long)pos[j] * D;
+    if (vec) {
+        for (int i = lane; i < D / 4; i += 32) {
+            const float4 x = reinterpret_cast<const float4*>(a)[i];
+            const float4 y = reinterpret_cast<const float4*>(b)[i];
+            float4 r;
+            r.x = alpha * x.x + beta * y.x;
+            r.y = alpha * x.y + beta * y.y;
+            r.z = alpha * x.z + beta * y.z;
+            r.w = alpha * x.w + beta * y.w;
+            reinterpret_cast<float4*>(o)[i] = r;
+        }
+    } else {
+        for (int i = lane; i < D; i += 32) o[i] = alpha * a[i] + beta * b[i];
+    }
+}
+
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_kernel(long long n, int D, int vec, const float* __restrict__ in, const float* __restrict__ gamma,
+                 float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= n) return;
+    const float* src = in + j * D;
+    float mean, rstd;
+    warp_row_stats(src, D, vec != 0, mean, rstd);
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 v = load_row4(src, base, D, vec != 0);
+        const float4 g = load_row4(gamma, base, D, vec != 0);
+        const float r[4] = {ln_apply(v.x, mean, rstd, g.x), ln_apply(v.y, mean, rstd, g.y),
+                            ln_apply(v.z, mean, rstd, g.z), ln_apply(v.w, mean, rstd, g.w)};
+        if (vec) {
+            *reinterpret_cast<float4*>(out + j * D + base) = make_float4(r[0], r[1], r[2], r[3]);
+        } else {
+            for (int k = 0; k < 4 && base + k < D; ++k) out[j * D + base + k] = r[k];
+        }
+    }
+}
+
+// h = LN(x; gamma) written as TF32 head / tail planes (rows already in place).
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+ln_split_kernel(long long n, int D, int vec, const float* __restrict__ in, const float* __restrict__ gamma,
+                float* __restrict__ h_hi, float* __restrict__ h_lo) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= n) return;
+    const float* src = in + j * D;
+    float mean, rstd;
+    warp_row_stats(src, D, vec != 0, mean, rstd);
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 v = load_row4(src, base, D, vec != 0);
+        const float4 g = load_row4(gamma, base, D, vec != 0);
+        const float r[4] = {ln_apply(v.x, mean, rstd, g.x), ln_apply(v.y, mean, rstd, g.y),
+                            ln_apply(v.z, mean, rstd, g.z), ln_apply(v.w, mean, rstd, g.w)};
+        for (int k = 0; k < 4 && base + k < D; ++k) split_tf32(r[k], h_hi[j * D + base + k], h_lo[j * D + base + k]);
+    }
+}
+
+__global__ void gelu_dot_kernel(const float* __restrict__ a, float* __restrict__ b, size_t len) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) b[i] = gelu_dot(a[i], b[i]);
+}
+
+// hi/lo planes of a raw FP32 array (weights at load time).
+__global__ void split_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                             size_t len4, size_t len) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len4; i += stride) {
+        const float4 v = reinterpret_cast<const float4*>(src)[i];
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
+        reinterpret_cast<float4*>(hi)[i] = h;
+        reinterpret_cast<float4*>(lo)[i] = l;
+    }
+    for (size_t i = len4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride)
+        split_tf32(src[i], hi[i], lo[i]);
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+inline unsigned row_grid(long long rows) { return (unsigned)((rows + ROW_WARPS - 1) / ROW_WARPS); }
+
+}  // namespace
+
+int launch_scatter(long long T, int D, const float* X, const float* coeff, const int* pos, float* routed,
+                   float* rcoeff, cudaStream_t stream) {
+    if (T < 0 || D <= 0 || !X || !pos || !routed) {
+        set_error("expert_scatter: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(X) && aligned16(routed);
+    scatter_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, coeff, pos, routed, rcoeff);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
+                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo,
+                            cudaStream_t stream) {
+    if (T == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(X) && aligned16(routed) && aligned16(h_hi) && aligned16(h_lo) &&
+                    aligned16(gamma_all);
+    scatter_ln_split_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate, gamma_all,
+                                                                        routed, rscore, h_hi, h_lo);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream) {
+    if (T < 0 || D <= 0 || !in || !pos || !out) {
+        set_error("expert_gather: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(in) && aligned16(out);
+    gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, in, pos, out);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_mix_gather(long long T, int D, const int* pos, const float* routed, const float* post,
+                      const float* coeff, float* out, cudaStream_t stream) {
+    if (T < 0 || D <= 0 || !pos || !routed || !post || !coeff || !out) {
+        set_error("expert_mix_gather: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (T == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(routed) && aligned16(post) && aligned16(out);
+    mix_gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, pos, routed, post, coeff, out);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_layernorm(float* out, const float* in, long long n, int D, const float* gamma, cudaStream_t stream) {
+    if (n < 0 || D <= 0 || !out || !in || !gamma) {
+        set_error("layernorm: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (n == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(in) && aligned16(out) && aligned16(gamma);
+    layernorm_kernel<<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, out);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
+                    cudaStream_t stream) {
+    if (n == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(in) && aligned16(gamma);
+    ln_split_kernel<<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, h_hi, h_lo);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_gelu_dot(const float* a, float* b, size_t len, cudaStream_t stream) {
+    if (!a || !b) {
+        set_error("gelu_dot: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (len == 0) return INFMOE_OK;
+    const unsigned grid = (unsigned)((len + 255) / 256 < 148 * 16 ? (len + 255) / 256 : 148 * 16);
+    gelu_dot_kernel<<<grid, 256, 0, stream>>>(a, b, len);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_t stream) {
+    if (len == 0) return INFMOE_OK;
+    const bool vec = aligned16(src) && aligned16(hi) && aligned16(lo);
+    const size_t len4 = vec ? len / 4 : 0;
+    const size_t work = len4 ? len4 : len;
+    const unsigned grid = (unsigned)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+    split_kernel<<<grid, 256, 0, stream>>>(src, hi, lo, len4, len);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+}  // namespace infmoe
