@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Benchmark of the MoE-layer hot path (MoELayerPlugin::enqueue) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one forward pass of the MoE layer over one batch of synthetic input.
+With N = 1 the workload is the CPM-2-style layer the headline metric is quoted on
+(E=32, d_model=4096, d_ff=10240, 8x512 tokens, all experts resident).  With N > 1
+(launched under torch.distributed.run, one rank per GPU) the experts are sharded
+expert-parallel, every rank keeps the same number of local tokens and local
+experts (weak scaling), and tokens move with an NCCL all-to-all.
+
+One JSON line is printed by rank 0.  `value` is whole-job tokens/s with the input
+already in HBM, timed on the device with CUDA events (max over ranks); `e2e` is
+the same metric through the host-buffer entry point of the C ABI with the
+host<->device copies inside the timed region.  `roofline` describes the dominant
+kernel (the gated wi_0/wi_1 grouped GEMM); `cpu_baseline` is the CPU restatement
+of the reference's math timed on this box's host cores on a bounded sample.
+
+--impl reference times that CPU restatement alone (the reference itself has no CPU
+path and its TensorRT plugin cannot be built here), on all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from infmoe_b200 import synth  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()      # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the restatement of the reference's math on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_setup(w: synth.Workload, sample_experts: int, tokens_per_expert: int):
+    """A bounded slice of workload `w`: `sample_experts` experts and the tokens they would get."""
+    from oracle import oracle
+
+    ws = synth.scaled(w, expert_count=sample_experts, batch=1, seq_len=sample_experts * tokens_per_expert)
+    x, cent, ln = synth.gen_inputs(ws)
+    experts = [synth.gen_expert_numpy(ws, e) for e in range(sample_experts)]
+    return oracle, ws, x, cent, ln, experts
+
+
+def cpu_step(oracle, ws, x, cent, ln, experts):
+    t0 = time.perf_counter()
+    oracle.layer_forward_f32(x, ws.variant, cent, ln, experts)
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_experts = 2 if w.embedding_size * w.hidden_size > (1 << 24) else min(w.expert_count, 4)
+    tpe = max(1, min(w.tokens // w.expert_count, 128))
+    oracle, ws, x, cent, ln, experts = cpu_sample_setup(w, sample_experts, tpe)
+    for _ in range(args.warmup):
+        cpu_step(oracle, ws, x, cent, ln, experts)
+    t = sum(cpu_step(oracle, ws, x, cent, ln, experts) for _ in range(args.steps))
+    value = ws.tokens * args.steps / t
+    sample = (f"{sample_experts} of {w.expert_count} experts x {tpe} tokens of workload {w.name} per step, "
+              f"weights in host memory")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's math (oracle/oracle.c, OpenMP + AVX2); the reference has no CPU "
+                "path and its TensorRT plugin cannot be built on this box",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(w, n_gpus):
+    return {"workload": w.name, "moe_variant": w.variant, "expert_count": w.expert_count * (n_gpus if n_gpus > 1 else 1),
+            "d_model": w.embedding_size, "d_ff": w.hidden_size,
+            "tokens": w.tokens * (n_gpus if n_gpus > 1 else 1), "experts": "streamed" if w.streamed else "resident",
+            "parallelism": f"ep{n_gpus}" if n_gpus > 1 else "single",
+            "l2": "expert weights (GBs) stream through L2 every step; nothing is flushed explicitly"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def build_layer(w, device, torch):
+    from infmoe_b200 import MoELayer
+
+    x, cent, ln = synth.gen_inputs(w)
+    layer = MoELayer.create(w.expert_count, w.embedding_size, w.hidden_size, w.max_concurrency, cent, None, "T5_FF",
+                            w.variant, ln)
+    if w.streamed:
+        for e in range(w.expert_count):
+            ws = [t.cpu().numpy() for t in synth.gen_expert_torch(w, e, device)]
+            layer.set_expert(e, *ws)
+        layer.set_residency(0)
+    else:
+        for e in range(w.expert_count):
+            layer.set_expert(e, *synth.gen_expert_torch(w, e, device))
+        layer.set_residency(1)
+    torch.cuda.synchronize()
+    return layer, x, cent, ln
+
+
+def run_single(args, w):
+    import torch
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = _peaks()
+    layer, x, cent, ln = build_layer(w, dev, torch)
+    T, D, F, E = w.tokens, w.embedding_size, w.hidden_size, w.expert_count
+    hx = torch.from_numpy(x).pin_memory()
+    hout = torch.empty_like(hx).pin_memory()
+    dx = hx.to(dev)
+    dout = torch.empty_like(dx)
+    stream = torch.cuda.current_stream()
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        layer.forward(dx, dout)
+    layer.sync_status(stream.cuda_stream)
+    layer.set_profiling(True)
+    launches0 = layer.kernel_launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clocks:
+        start.record(stream)
+        for _ in range(args.steps):
+            layer.forward(dx, dout)
+        stop.record(stream)
+        torch.cuda.synchronize()
+    layer.sync_status(stream.cuda_stream)
+    ms = start.elapsed_time(stop) / args.steps
+    launches = layer.kernel_launches - launches0
+    stage_ms, calls = layer.stage_ms()
+    layer.set_profiling(False)
+
+    # ---- end to end through the host-buffer entry point ----
+    for _ in range(min(args.warmup, 3)):
+        layer.forward_host_ptr(hx.data_ptr(), hout.data_ptr(), T)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        layer.forward_host_ptr(hx.data_ptr(), hout.data_ptr(), T)
+    e2e_s = (time.perf_counter() - t0) / args.steps
+
+    # ---- roofline of the dominant kernel (expert GEMM 1: wi_0 / wi_1 + gelu) ----
+    gate_p = layer.last_routing()[0]
+    from infmoe_b200.devmem import read_device
+    gate = read_device(gate_p, T, np.int32)
+    active = int(np.count_nonzero(np.bincount(gate, minlength=E)))
+    g1_ms = stage_ms["ffn_gemm1"] if stage_ms["ffn_gemm1"] > 0 else None
+    useful_flops = 4.0 * T * D * F                    # algorithmic flops of h wi_0^T and h wi_1^T
+    peak_3xtf32 = peaks["bf16_sustained"] / 6.0       # TF32 = bf16 / 2, three MMAs per product
+    roofline = None
+    if g1_ms:
+        achieved = useful_flops / (g1_ms * 1e-3) / 1e12
+        weight_bytes = 2.0 * (2 * D * F * 4) * active  # head + tail planes of the interleaved wi_0/wi_1 matrix
+        roofline = {"kernel": "ffn_umma_kernel<EPI_GELU_PAIR>", "bound": "tensor", "achieved": achieved,
+                    "peak": peak_3xtf32, "unit": "TFLOP/s", "frac": achieved / peak_3xtf32, "traffic": None,
+                    "peak_source": f"bf16 sustained {peaks['bf16_sustained']} TFLOP/s of {peaks['source']} / 6 "
+                                   "(TF32 = bf16/2, 3 MMAs per product)",
+                    "ms": g1_ms, "weight_stream_gbs": weight_bytes / (g1_ms * 1e-3) / 1e9,
+                    "hbm_peak_gbs": peaks["hbm_gbs"]}
+
+    # ---- CPU baseline on a bounded sample ----
+    cpu = None
+    if not args.no_cpu:
+        sample_experts = 2
+        tpe = max(1, min(T // E, 128))
+        oracle, ws, cx, ccent, cln, cexp = cpu_sample_setup(w, sample_experts, tpe)
+        cpu_step(oracle, ws, cx, ccent, cln, cexp)
+        reps, t = 0, 0.0
+        while t < 10.0 and reps < 20:
+            t += cpu_step(oracle, ws, cx, ccent, cln, cexp)
+            reps += 1
+        cpu = {"value": ws.tokens * reps / t, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"{sample_experts} of {E} experts x {tpe} tokens of workload {w.name}, {reps} passes"}
+
+    line = {
+        "metric": METRIC, "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (3xTF32 tensor-core products, FP32 accumulate)", "data": "synthetic",
+        "config": workload_config(w, 1),
+        "e2e": {"value": T / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(hx.numel() * 4),
+                "d2h_bytes_per_step": int(hout.numel() * 4), "ms_per_step": 1e3 * e2e_s},
+        "gpu_launches": int(launches), "stage_ms": stage_ms, "active_experts": active,
+        "ffn_useful_tflops": 6.0 * T * D * F / ((stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) * 1e-3) / 1e12
+        if (stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) > 0 else None,
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    layer.terminate()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    name = args.workload or ("cpm2" if args.gpus == 1 else "ep_cpm2")
+    w = synth.WORKLOADS[name]
+    if args.impl == "reference":
+        if args.gpus > 1:
+            w = ep_local_workload(w, args.gpus)
+        run_reference_arm(args, w)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_single(args, w)
+    else:
+        from infmoe_b200 import ep_bench
+        ep_bench.run(args, w, METRIC, UNIT, ClockSampler, _peaks, workload_config)
+
+
+def ep_local_workload(w, n):
+    """Per-rank share of the expert-parallel workload (weak scaling: fixed per-GPU work)."""
+    return w
+
+
+if __name__ == "__main__":
+    main()

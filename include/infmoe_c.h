@@ -113,6 +113,15 @@ INFMOE_API int infmoe_layer_forward_host(infmoe_layer* layer, const float* h_inp
 INFMOE_API int infmoe_layer_last_routing(const infmoe_layer* layer, const int32_t** d_gate, const float** d_score,
                                          const int32_t** d_pos, const int32_t** d_count, const int32_t** d_offset);
 
+/* Per-stage device timing.  When enabled, enqueue records CUDA events on the
+ * caller's stream around its stages (a ring of the last 64 calls).
+ * infmoe_layer_stage_ms waits for those calls and returns the average
+ * milliseconds of: routing, dispatch, scatter, expert GEMM 1 (wi_0/wi_1 + gelu),
+ * expert GEMM 2 (wo + residual), combine -- ms[6] -- then restarts the ring.
+ * With streamed experts the two GEMM entries are reported together in ms[3]. */
+INFMOE_API int infmoe_layer_set_profiling(infmoe_layer* layer, int enable);
+INFMOE_API int infmoe_layer_stage_ms(infmoe_layer* layer, float* ms, int32_t* calls);
+
 /* Number of kernels this library launched on behalf of `layer` so far. */
 INFMOE_API int64_t infmoe_layer_kernel_launches(const infmoe_layer* layer);
 

@@ -65,6 +65,8 @@ SIGNATURES = {
     "infmoe_layer_forward_host": [_vp, _vp, _vp, _i64],
     "infmoe_layer_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,
     "infmoe_layer_kernel_launches": [_vp],
+    "infmoe_layer_set_profiling": [_vp, ctypes.c_int],
+    "infmoe_layer_stage_ms": [_vp, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i32)],
     "infmoe_layer_destroy": [_vp],
     "infmoe_layer_serialization_size": [_vp, ctypes.POINTER(_sz)],
     "infmoe_layer_serialize": [_vp, _vp, _sz],

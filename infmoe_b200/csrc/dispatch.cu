@@ -107,7 +107,7 @@ size_t dispatch_smem_bytes(int E) { return sizeof(int) * (size_t)(2 + DISPATCH_W
 
 int launch_dispatch(const int* gate, long long T, int E, int* pos, int* count, int* offset, int* status,
                     cudaStream_t stream) {
-    if (T < 0 || T > 0x7fffffffLL || E <= 0 || !gate || !pos || !count || !offset) {
+    if (T < 0 || T > 0x7fffffffLL || E <= 0 || (T > 0 && (!gate || !pos)) || !count || !offset) {
         set_error("expert_count: bad argument (T=%lld E=%d)", T, E);
         return INFMOE_ERR_INVALID_ARGUMENT;
     }

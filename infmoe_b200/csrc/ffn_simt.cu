@@ -9,7 +9,8 @@
 //   g = gelu(h wi_0^T) * (h wi_1^T)        h = h_hi + h_lo (exact recombination)
 //   y = x + g wo^T
 // Operands are stored as TF32 head/tail planes; head + tail is the original
-// FP32 value exactly, so these kernels compute with full FP32 inputs.
+// FP32 value exactly, so these kernels compute with full FP32 inputs.  wi_0 and
+// wi_1 share one plane pair with interleaved rows (row 2f = wi_0[f], 2f+1 = wi_1[f]).
 #include "common.cuh"
 
 namespace infmoe {
@@ -43,8 +44,7 @@ template <bool DUAL>
 __global__ void __launch_bounds__(256)
 ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, int K,
                 const float* __restrict__ a_hi, const float* __restrict__ a_lo,
-                const float* __restrict__ w0_hi, const float* __restrict__ w0_lo,
-                const float* __restrict__ w1_hi, const float* __restrict__ w1_lo,
+                const float* __restrict__ w_hi, const float* __restrict__ w_lo,
                 const int* __restrict__ slot_of_expert, const float* __restrict__ resid,
                 float* __restrict__ out_hi, float* __restrict__ out_lo) {
     __shared__ float As[TK][TM + 1];
@@ -64,7 +64,7 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
     const int expert = s_info[1], row0 = s_info[2], rows = s_info[3];
     const int slot = slot_of_expert ? slot_of_expert[expert] : expert;
     const int n0 = blockIdx.x * TN;
-    const size_t wbase = (size_t)slot * (size_t)N * (size_t)K;
+    const size_t wbase = (size_t)slot * (size_t)N * (size_t)K * (DUAL ? 2 : 1);
 
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     float acc0[4][4], acc1[4][4];
@@ -87,9 +87,9 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
             const int n = i / TK, k = i % TK;
             float v0 = 0.f, v1 = 0.f;
             if (n0 + n < N && k0 + k < K) {
-                const size_t o = wbase + (size_t)(n0 + n) * K + k0 + k;
-                v0 = w0_hi[o] + w0_lo[o];
-                if (DUAL) v1 = w1_hi[o] + w1_lo[o];
+                const size_t o = wbase + (size_t)(n0 + n) * K * (DUAL ? 2 : 1) + k0 + k;
+                v0 = w_hi[o] + w_lo[o];
+                if (DUAL) v1 = w_hi[o + K] + w_lo[o + K];
             }
             B0s[k][n] = v0;
             if (DUAL) B1s[k][n] = v1;
@@ -140,18 +140,17 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
 
 // Grouped FFN over experts [e_begin, e_end); T rows in expert-contiguous order.
 //   h_hi/h_lo [T][D], g_hi/g_lo [T][F] (scratch), routed [T][D], post [T][D]
-//   weights: planes [slots][F][D] (wi_0, wi_1) and [slots][D][F] (wo);
 //   slot_of_expert (device, may be NULL = identity) maps expert -> weight slot.
 int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
-                    const float* h_hi, const float* h_lo, const float* w0_hi, const float* w0_lo,
-                    const float* w1_hi, const float* w1_lo, const float* wo_hi, const float* wo_lo,
-                    const float* routed, float* g_hi, float* g_lo, float* post, cudaStream_t stream) {
+                    const float* h_hi, const float* h_lo, const float* w01_hi, const float* w01_lo,
+                    const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi, float* g_lo,
+                    float* post, cudaStream_t stream) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     const unsigned row_tiles = (unsigned)((T + TM - 1) / TM + (e_end - e_begin));
     dim3 g1((F + TN - 1) / TN, row_tiles), g2((D + TN - 1) / TN, row_tiles);
-    ffn_simt_kernel<true><<<g1, 256, 0, stream>>>(offset, e_begin, e_end, F, D, h_hi, h_lo, w0_hi, w0_lo, w1_hi, w1_lo,
+    ffn_simt_kernel<true><<<g1, 256, 0, stream>>>(offset, e_begin, e_end, F, D, h_hi, h_lo, w01_hi, w01_lo,
                                                   slot_of_expert, nullptr, g_hi, g_lo);
-    ffn_simt_kernel<false><<<g2, 256, 0, stream>>>(offset, e_begin, e_end, D, F, g_hi, g_lo, wo_hi, wo_lo, nullptr, nullptr,
+    ffn_simt_kernel<false><<<g2, 256, 0, stream>>>(offset, e_begin, e_end, D, F, g_hi, g_lo, wo_hi, wo_lo,
                                                    slot_of_expert, routed, post, nullptr);
     note_launch(2);
     INFMOE_CUDA_TRY(cudaGetLastError());

@@ -6,9 +6,11 @@
 // T5FFLayer::run (plugin/sublayers/T5FFLayer.cc:112-138):
 //   cublasSgemm_v2 x2 (wi_0, wi_1) -> fused_gelu_dot_gpu -> cudaMemcpyAsync D2D -> cublasSgemm_v2 (beta = 1)
 //
-// Two launches of one kernel template:
-//   DUAL = true   g = gelu(h wi_0^T) * (h wi_1^T)    K = d_model, weight rows = d_ff
-//   DUAL = false  y = x + g wo^T                     K = d_ff,    weight rows = d_model
+// Two launches of one kernel template (the weights are the M-side operand):
+//   EPI_GELU_PAIR  g = gelu(h wi_0^T) * (h wi_1^T)   K = d_model, weight rows = 2 * d_ff
+//                  (rows of wi_0 and wi_1 are stored interleaved: row 2f = wi_0[f], row 2f+1 = wi_1[f],
+//                   so both halves of the gate land in neighbouring TMEM lanes of ONE accumulator)
+//   EPI_RESIDUAL   y = x + g wo^T                     K = d_ff,    weight rows = d_model
 //
 // Orientation.  Weight rows sit on the MMA's M side (always a full 128-row
 // tile), the tokens of one expert on the N side (any multiple of 16 up to
@@ -21,15 +23,25 @@
 // lo*hi + hi*lo + hi*hi into the same FP32 accumulator; the dropped lo*lo term
 // is below 2^-22 relative.
 //
-// Pipeline per CTA (persistent, one CTA per SM, 192 threads):
-//   warp 0      TMA producer: per k block loads the weight tiles (box 128 x BK)
-//               and the token tiles (boxes 32 x BK) of both planes into a
+// Chunked accumulation.  The tensor core adds into its FP32 accumulator with
+// truncation, not round-to-nearest: measured on B200, one accumulator carried
+// over K = 1024..2048 drifts by about 1.5e-5 relative, and the drift grows
+// linearly with the number of MMAs.  So TMEM only ever holds the sum of one K
+// chunk of 256 (96 MMAs); two TMEM accumulators alternate, and the accumulate
+// warps add each finished chunk into a running sum in registers with
+// round-to-nearest adds while the tensor core already works on the next chunk.
+// The same double buffering hides the epilogue behind the next tile's MMAs.
+//
+// Pipeline per CTA (persistent, one CTA per SM, 320 threads):
+//   warp 0      TMA producer: per k block loads the weight tile (box 128 x BK)
+//               and the token tile (boxes 32 x BK) of both planes into a
 //               STAGES-deep shared-memory ring, completion on mbarriers
 //   warp 1      allocates TMEM, issues tcgen05.mma from one lane, commits each
-//               stage back to the producer and the finished tile to the epilogue
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane quarter per
-//               warp), gelu*dot + TF32 split (DUAL) or residual add, coalesced
-//               128-byte stores (32 consecutive weight rows of one token)
+//               stage back to the producer and each K chunk to the accumulate warps
+//   warps 2..9  accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter
+//               and every other 16-column slice per warp), add into registers; after
+//               the last chunk gelu*dot + TF32 split (lane pairs exchange a and b by
+//               shuffle) or residual add, stores contiguous over the weight-row index
 // Tiles are (expert, 128-row weight block, token chunk); the list is derived in
 // the kernel from offset[E+1], so no host synchronisation is needed.  Every
 // mbarrier wait is bounded: on expiry the CTA raises STATUS_WAIT_TIMEOUT, lets
@@ -43,7 +55,6 @@ namespace infmoe {
 namespace {
 
 constexpr int UMMA_M = 128;
-constexpr int GEMM_THREADS = 192;
 constexpr int MAX_EXPERTS = 1024;
 constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;  // 4 s
 
@@ -159,16 +170,23 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UMMA_M >> 4) << 24);
 }
 
-template <bool DUAL, int BK, int NMAX, int STAGES>
+enum { EPI_GELU_PAIR = 0, EPI_RESIDUAL = 1 };
+
+constexpr int EPI_WARPS = 8;                        // two warps per TMEM lane quarter
+constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;  // producer, MMA issuer, accumulate/epilogue warps
+constexpr int ACC_STRIDE = 256;                     // TMEM columns between the two accumulator buffers
+constexpr int TMEM_COLS = 512;
+constexpr int K_CHUNK = 256;                        // K extent accumulated inside the tensor core at a time
+
+template <int BK, int NMAX, int STAGES>
 struct Cfg {
-    static constexpr int NW = DUAL ? 4 : 2;                         // weight tiles per stage
     static constexpr int W_TILE = UMMA_M * BK * 4;
     static constexpr int A_TILE = NMAX * BK * 4;
-    static constexpr int STAGE = NW * W_TILE + 2 * A_TILE;
-    static constexpr int B_COL = 256;                                // TMEM column of the second accumulator
-    static constexpr int TMEM_COLS = DUAL ? 512 : 256;
+    static constexpr int STAGE = 2 * W_TILE + 2 * A_TILE;           // hi and lo planes of both operands
     static constexpr int SMEM = STAGES * STAGE + 1024;              // + slack to align the ring to 1024 bytes
-    static_assert(NMAX % 32 == 0 && NMAX <= 256, "token chunk");
+    static constexpr int KB_PER_CHUNK = K_CHUNK / BK;
+    static constexpr int SLICES = NMAX / 32;                        // 16-column slices owned by one epilogue thread
+    static_assert(NMAX % 32 == 0 && NMAX <= ACC_STRIDE, "token chunk");
     static_assert(W_TILE % 1024 == 0 && A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
 };
 
@@ -176,11 +194,11 @@ struct GemmArgs {
     const int* offset;          // [E+1] first routed row of each expert
     const int* slot_of_expert;  // expert -> weight slot (NULL: identity)
     int E, e_begin, e_end;      // experts [e_begin, e_end) are processed
-    int M_total;                // weight rows (d_ff for DUAL, d_model otherwise)
+    int M_total;                // weight rows: 2 * d_ff (wi_0 / wi_1 rows interleaved) or d_model
     int K;
-    float* out_hi;              // DUAL: g_hi [T][M_total]; else y [T][M_total]
-    float* out_lo;              // DUAL: g_lo
-    const float* resid;         // !DUAL: x [T][M_total]
+    float* out_hi;              // GELU_PAIR: g_hi [T][M_total / 2]; RESIDUAL: y [T][M_total]
+    float* out_lo;              // GELU_PAIR: g_lo
+    const float* resid;         // RESIDUAL: x [T][M_total]
     int* status;
 };
 
@@ -195,7 +213,7 @@ __device__ __forceinline__ void chunking(int cnt, int& nch, int& csz) {
 }
 
 template <int NMAX>
-__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, const GemmArgs& a, int MB) {
+__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, const GemmArgs& a) {
     int lo = a.e_begin, hi = a.e_end - 1;  // last e with s_prefix[e] <= tile
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
@@ -213,22 +231,20 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, c
     t.row0 = beg + c * csz;
     t.n_tok = min(csz, beg + cnt - t.row0);
     t.n_pad = (t.n_tok + 15) & ~15;
-    (void)MB;
     return t;
 }
 
-template <bool DUAL, int BK, int NMAX, int STAGES>
+template <int EPI, int BK, int NMAX, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w0_hi, const __grid_constant__ CUtensorMap map_w0_lo,
-                const __grid_constant__ CUtensorMap map_w1_hi, const __grid_constant__ CUtensorMap map_w1_lo,
+ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
                 const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                 const GemmArgs args) {
-    using C = Cfg<DUAL, BK, NMAX, STAGES>;
+    using C = Cfg<BK, NMAX, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[STAGES];
     __shared__ __align__(8) uint64_t s_empty[STAGES];
-    __shared__ __align__(8) uint64_t s_acc_full;
-    __shared__ __align__(8) uint64_t s_acc_empty;
+    __shared__ __align__(8) uint64_t s_acc_full[2];
+    __shared__ __align__(8) uint64_t s_acc_empty[2];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_prefix[MAX_EXPERTS + 1];
@@ -266,14 +282,16 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w0_hi, const __grid_cons
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&s_empty[s]), 1);
         }
-        mbar_init(smem_u32(&s_acc_full), 1);
-        mbar_init(smem_u32(&s_acc_empty), 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&s_acc_full[b]), 1);
+            mbar_init(smem_u32(&s_acc_empty[b]), EPI_WARPS * 32);
+        }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
-                     "r"((uint32_t)C::TMEM_COLS)
+                     "r"((uint32_t)TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -289,103 +307,137 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w0_hi, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args, MB);
+                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
                 const int nbox = (t.n_pad + 31) >> 5;
-                const uint32_t bytes = C::NW * C::W_TILE + 2 * nbox * 32 * BK * 4;
+                const uint32_t bytes = 2 * C::W_TILE + 2 * nbox * 32 * BK * 4;
+                bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1, abort_flag)) break;
+                    if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&s_full[s]);
                     mbar_expect_tx(bar, bytes);
                     const uint32_t base = ring + s * C::STAGE;
                     const int k0 = kb * BK, m0 = t.mb * UMMA_M;
-                    tma_load_3d(base + 0 * C::W_TILE, &map_w0_hi, bar, k0, m0, t.slot);
-                    tma_load_3d(base + 1 * C::W_TILE, &map_w0_lo, bar, k0, m0, t.slot);
-                    if (DUAL) {
-                        tma_load_3d(base + 2 * C::W_TILE, &map_w1_hi, bar, k0, m0, t.slot);
-                        tma_load_3d(base + 3 * C::W_TILE, &map_w1_lo, bar, k0, m0, t.slot);
-                    }
-                    const uint32_t a_hi = base + C::NW * C::W_TILE, a_lo = a_hi + C::A_TILE;
+                    tma_load_3d(base, &map_w_hi, bar, k0, m0, t.slot);
+                    tma_load_3d(base + C::W_TILE, &map_w_lo, bar, k0, m0, t.slot);
+                    const uint32_t a_hi = base + 2 * C::W_TILE, a_lo = a_hi + C::A_TILE;
                     for (int b = 0; b < nbox; ++b) {
                         tma_load_2d(a_hi + b * 32 * BK * 4, &map_a_hi, bar, k0, t.row0 + b * 32);
                         tma_load_2d(a_lo + b * 32 * BK * 4, &map_a_lo, bar, k0, t.row0 + b * 32);
                     }
                 }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args, MB);
+            uint32_t it = 0, chunk = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
                 const uint32_t idesc = make_idesc(t.n_pad);
-                if (!mbar_wait(smem_u32(&s_acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
-                tc_fence_after();
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int kc = kb % C::KB_PER_CHUNK;
+                    const uint32_t buf = chunk & 1;
+                    if (kc == 0) {  // a new K chunk starts in accumulator `buf`: it must have been drained
+                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), ((chunk >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                    }
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t base = ring + s * C::STAGE;
-                    const uint32_t a_hi = base + C::NW * C::W_TILE, a_lo = a_hi + C::A_TILE;
+                    const uint32_t a_hi = base + 2 * C::W_TILE, a_lo = a_hi + C::A_TILE;
+                    const uint32_t d = tmem_base + buf * ACC_STRIDE;
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ++ks) {
                         const uint32_t koff = ks * 32;  // 8 TF32 = 32 bytes along K inside the swizzled row
                         const uint64_t d_a_hi = make_smem_desc<BK>(a_hi + koff);
                         const uint64_t d_a_lo = make_smem_desc<BK>(a_lo + koff);
-                        const uint32_t first = (kb | ks) ? 1u : 0u;
-#pragma unroll
-                        for (int w = 0; w < (DUAL ? 2 : 1); ++w) {
-                            const uint64_t d_w_hi = make_smem_desc<BK>(base + (2 * w + 0) * C::W_TILE + koff);
-                            const uint64_t d_w_lo = make_smem_desc<BK>(base + (2 * w + 1) * C::W_TILE + koff);
-                            const uint32_t d = tmem_base + w * C::B_COL;
-                            umma_tf32(d, d_w_lo, d_a_hi, idesc, first);   // small terms first
-                            umma_tf32(d, d_w_hi, d_a_lo, idesc, 1u);
-                            umma_tf32(d, d_w_hi, d_a_hi, idesc, 1u);
-                        }
+                        const uint64_t d_w_hi = make_smem_desc<BK>(base + koff);
+                        const uint64_t d_w_lo = make_smem_desc<BK>(base + C::W_TILE + koff);
+                        umma_tf32(d, d_w_lo, d_a_hi, idesc, (kc | ks) ? 1u : 0u);   // small terms first
+                        umma_tf32(d, d_w_hi, d_a_lo, idesc, 1u);
+                        umma_tf32(d, d_w_hi, d_a_hi, idesc, 1u);
                     }
                     umma_commit(smem_u32(&s_empty[s]));  // stage reusable once these MMAs have read it
+                    if (kc == C::KB_PER_CHUNK - 1 || kb == KB - 1) {
+                        umma_commit(smem_u32(&s_acc_full[buf]));  // chunk complete: hand it to the accumulate warps
+                        ++chunk;
+                    }
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&s_acc_full));
             }
         }
     } else {
-        // ================= epilogue (warps 2..5) =================
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        uint32_t tcount = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args, MB);
-            if (!mbar_wait(smem_u32(&s_acc_full), tcount & 1, abort_flag)) break;
-            tc_fence_after();
+        // ================= accumulate + epilogue (warps 2..9) =================
+        // The tensor core adds into its FP32 accumulator with truncation, so a long K loop inside
+        // TMEM drifts.  Each K chunk is therefore accumulated from zero in TMEM and added to a
+        // running sum in registers with round-to-nearest adds.
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;       // even or odd 16-column slices
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t chunk = 0;
+        const int NC = (KB + C::KB_PER_CHUNK - 1) / C::KB_PER_CHUNK;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+            const int nsl = t.n_pad >> 4;
+            float sum[C::SLICES][16];
+#pragma unroll
+            for (int i = 0; i < C::SLICES; ++i)
+#pragma unroll
+                for (int c = 0; c < 16; ++c) sum[i][c] = 0.f;
+            bool ok = true;
+            for (int ch = 0; ch < NC; ++ch, ++chunk) {
+                const uint32_t buf = chunk & 1;
+                if (!mbar_wait(smem_u32(&s_acc_full[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int i = 0; i < C::SLICES; ++i) {
+                    const int sl = 2 * i + half;
+                    if (sl < nsl) {
+                        uint32_t r[16];
+                        tmem_ld16(tlane + buf * ACC_STRIDE + sl * 16, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) sum[i][c] = __fadd_rn(sum[i][c], __uint_as_float(r[c]));
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(smem_u32(&s_acc_empty[buf]));
+            }
+            if (!ok) break;
             const int m = t.mb * UMMA_M + q * 32 + lane;
             const bool m_ok = m < args.M_total;
-            const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
-            for (int c0 = 0; c0 < t.n_pad; c0 += 16) {
-                uint32_t ra[16], rb[16];
-                tmem_ld16(tlane + c0, ra);
-                if (DUAL) tmem_ld16(tlane + C::B_COL + c0, rb);
-                tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < C::SLICES; ++i) {
+                const int sl = 2 * i + half;
+                if (sl >= nsl) continue;     // uniform across the warp
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    if (c0 + c < t.n_tok && m_ok) {
-                        const size_t o = (size_t)(t.row0 + c0 + c) * args.M_total + m;
-                        if (DUAL) {
-                            float hi, lo;
-                            split_tf32(gelu_dot(__uint_as_float(ra[c]), __uint_as_float(rb[c])), hi, lo);
-                            args.out_hi[o] = hi;
-                            args.out_lo[o] = lo;
-                        } else {
-                            args.out_hi[o] = args.resid[o] + __uint_as_float(ra[c]);
+                    const int col = sl * 16 + c;
+                    const float v = sum[i][c];
+                    if (EPI == EPI_GELU_PAIR) {
+                        // even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index
+                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                        const float a = (lane & 1) ? other : v, b = (lane & 1) ? v : other;
+                        float hi, lo;
+                        split_tf32(gelu_dot(a, b), hi, lo);
+                        if (col < t.n_tok && m_ok) {
+                            const size_t o = (size_t)(t.row0 + col) * (size_t)(args.M_total >> 1) + (size_t)(m >> 1);
+                            if (lane & 1) args.out_lo[o] = lo; else args.out_hi[o] = hi;
+                        }
+                    } else {
+                        if (col < t.n_tok && m_ok) {
+                            const size_t o = (size_t)(t.row0 + col) * (size_t)args.M_total + (size_t)m;
+                            args.out_hi[o] = __fadd_rn(args.resid[o], v);
                         }
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(smem_u32(&s_acc_empty));
         }
     }
 
@@ -401,8 +453,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w0_hi, const __grid_cons
     }
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"((uint32_t)C::TMEM_COLS)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                      : "memory");
     }
 }
@@ -450,22 +501,19 @@ int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uin
     return INFMOE_OK;
 }
 
-template <bool DUAL, int BK, int NMAX, int STAGES>
-int launch_one(const GemmArgs& args, long long T, int slots, const float* w0_hi, const float* w0_lo,
-               const float* w1_hi, const float* w1_lo, const float* a_hi, const float* a_lo, int num_ctas,
-               cudaStream_t stream) {
-    using C = Cfg<DUAL, BK, NMAX, STAGES>;
-    static_assert(C::SMEM <= 227 * 1024, "shared-memory ring too large");
-    CUtensorMap m[6];
-    INFMOE_TRY(make_map(&m[0], w0_hi, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[1], w0_lo, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[2], w1_hi, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[3], w1_lo, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[4], a_hi, args.K, (uint64_t)T, 1, BK, 32, 2));
-    INFMOE_TRY(make_map(&m[5], a_lo, args.K, (uint64_t)T, 1, BK, 32, 2));
-    auto kern = ffn_umma_kernel<DUAL, BK, NMAX, STAGES>;
+template <int EPI, int BK, int NMAX, int STAGES>
+int launch_one(const GemmArgs& args, long long T, int slots, const float* w_hi, const float* w_lo, const float* a_hi,
+               const float* a_lo, int num_ctas, cudaStream_t stream) {
+    using C = Cfg<BK, NMAX, STAGES>;
+    static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory ring too large");
+    CUtensorMap m[4];
+    INFMOE_TRY(make_map(&m[0], w_hi, args.K, args.M_total, slots, BK, UMMA_M, 3));
+    INFMOE_TRY(make_map(&m[1], w_lo, args.K, args.M_total, slots, BK, UMMA_M, 3));
+    INFMOE_TRY(make_map(&m[2], a_hi, args.K, (uint64_t)T, 1, BK, 32, 2));
+    INFMOE_TRY(make_map(&m[3], a_lo, args.K, (uint64_t)T, 1, BK, 32, 2));
+    auto kern = ffn_umma_kernel<EPI, BK, NMAX, STAGES>;
     INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], m[4], m[5], args);
+    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], args);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -477,12 +525,13 @@ bool ffn_umma_supported(int D, int F, int E) {
     return D % 4 == 0 && F % 4 == 0 && D >= 8 && F >= 8 && E <= MAX_EXPERTS;
 }
 
-// Same contract as launch_ffn_simt, restricted to experts [e_begin, e_end).
+// Grouped FFN over experts [e_begin, e_end); T rows in expert-contiguous order.
+//   h_hi/h_lo [T][D], g_hi/g_lo [T][F] (scratch), routed [T][D], post [T][D]
+//   w01 planes [slots][2F][D]: row 2f = wi_0[f], row 2f+1 = wi_1[f];  wo planes [slots][D][F]
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
-                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w0_hi,
-                    const float* w0_lo, const float* w1_hi, const float* w1_lo, const float* wo_hi,
-                    const float* wo_lo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
-                    int num_sms, cudaStream_t stream) {
+                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01_hi,
+                    const float* w01_lo, const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi,
+                    float* g_lo, float* post, int* status, int num_sms, cudaStream_t stream, cudaEvent_t mid_event) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     if (!ffn_umma_supported(D, F, E)) {
         set_error("ffn_umma: unsupported shape D=%d F=%d E=%d", D, F, E);
@@ -494,20 +543,21 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a1.E = E;
     a1.e_begin = e_begin;
     a1.e_end = e_end;
-    a1.M_total = F;
+    a1.M_total = 2 * F;
     a1.K = D;
     a1.out_hi = g_hi;
     a1.out_lo = g_lo;
     a1.resid = nullptr;
     a1.status = status;
-    INFMOE_TRY((launch_one<true, 16, 192, 3>(a1, T, slots, w0_hi, w0_lo, w1_hi, w1_lo, h_hi, h_lo, num_sms, stream)));
+    INFMOE_TRY((launch_one<EPI_GELU_PAIR, 16, 192, 5>(a1, T, slots, w01_hi, w01_lo, h_hi, h_lo, num_sms, stream)));
+    if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));
     GemmArgs a2 = a1;
     a2.M_total = D;
     a2.K = F;
     a2.out_hi = post;
     a2.out_lo = nullptr;
     a2.resid = routed;
-    INFMOE_TRY((launch_one<false, 16, 192, 5>(a2, T, slots, wo_hi, wo_lo, wo_hi, wo_lo, g_hi, g_lo, num_sms, stream)));
+    INFMOE_TRY((launch_one<EPI_RESIDUAL, 16, 192, 5>(a2, T, slots, wo_hi, wo_lo, g_hi, g_lo, num_sms, stream)));
     return INFMOE_OK;
 }
 

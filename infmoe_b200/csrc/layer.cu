@@ -63,12 +63,15 @@ struct ExpertStore {
     // device: LayerNorm weights of all experts [E][D] (always resident, 4*E*D bytes)
     float* d_ln = nullptr;
     std::vector<char> ln_on_device;
-    // device-resident TF32 head/tail planes: w0_hi, w0_lo, w1_hi, w1_lo, wo_hi, wo_lo, each [E][F*D]
-    float* d_plane[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // device-resident TF32 head/tail planes:
+    //   [0],[1] w01_hi, w01_lo [E][2F][D]  (row 2f = wi_0[f], row 2f+1 = wi_1[f])
+    //   [2],[3] wo_hi,  wo_lo  [E][D][F]
+    float* d_plane[4] = {nullptr, nullptr, nullptr, nullptr};
     std::vector<char> on_device;
     bool fortran_warning = false;
 
     size_t matrix_elems() const { return (size_t)D * (size_t)F; }
+    size_t plane_elems(int p) const { return (p < 2 ? 2 : 1) * matrix_elems(); }   // per expert
     size_t resident_bytes() const { return 6 * matrix_elems() * (size_t)E * sizeof(float); }
 
     ~ExpertStore() {
@@ -132,6 +135,11 @@ struct infmoe_layer {
     cudaStream_t own_stream = nullptr;
 
     long long launches_at_create = 0;
+
+    // optional per-stage timing: a ring of CUDA events recorded on the caller's stream
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;   // [PROF_CALLS][PROF_MARKS]
+    int prof_calls = 0;
 };
 
 namespace {
@@ -197,25 +205,33 @@ int ensure_store_device_ln(ExpertStore* s) {
 }
 
 int ensure_resident_planes(ExpertStore* s) {
-    for (int p = 0; p < 6; ++p)
-        if (!s->d_plane[p]) INFMOE_CUDA_TRY(cudaMalloc(&s->d_plane[p], sizeof(float) * s->matrix_elems() * s->E));
+    for (int p = 0; p < 4; ++p)
+        if (!s->d_plane[p]) INFMOE_CUDA_TRY(cudaMalloc(&s->d_plane[p], sizeof(float) * s->plane_elems(p) * s->E));
     return INFMOE_OK;
 }
 
-// Uploads every expert that is on the host but not yet on the device (raw copy into the
-// head plane, then an in-place head/tail split).
+// Puts one expert's raw matrices into its four planes: wi_0 / wi_1 rows interleaved into the
+// w01 head plane by two strided copies, wo into its head plane, then an in-place head/tail split.
+int load_expert_planes(int D, int F, const float* wi0, const float* wi1, const float* wo, float* w01_hi,
+                       float* w01_lo, float* wo_hi, float* wo_lo, cudaMemcpyKind kind, cudaStream_t stream) {
+    const size_t row = sizeof(float) * (size_t)D;
+    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01_hi, 2 * row, wi0, row, row, (size_t)F, kind, stream));
+    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01_hi + D, 2 * row, wi1, row, row, (size_t)F, kind, stream));
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(wo_hi, wo, sizeof(float) * (size_t)D * F, kind, stream));
+    INFMOE_TRY(launch_split(w01_hi, w01_hi, w01_lo, 2 * (size_t)D * F, stream));
+    INFMOE_TRY(launch_split(wo_hi, wo_hi, wo_lo, (size_t)D * F, stream));
+    return INFMOE_OK;
+}
+
+// Uploads every expert that is on the host but not yet on the device.
 int upload_resident(ExpertStore* s, cudaStream_t stream) {
     INFMOE_TRY(ensure_resident_planes(s));
     const size_t n = s->matrix_elems();
     for (int e = 0; e < s->E; ++e) {
         if (s->on_device[e] || !s->on_host[e]) continue;
-        const float* src[3] = {s->h_wi0[e], s->h_wi1[e], s->h_wo[e]};
-        for (int m = 0; m < 3; ++m) {
-            float* hi = s->d_plane[2 * m] + (size_t)e * n;
-            float* lo = s->d_plane[2 * m + 1] + (size_t)e * n;
-            INFMOE_CUDA_TRY(cudaMemcpyAsync(hi, src[m], sizeof(float) * n, cudaMemcpyHostToDevice, stream));
-            INFMOE_TRY(launch_split(hi, hi, lo, n, stream));
-        }
+        INFMOE_TRY(load_expert_planes(s->D, s->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e], s->d_plane[0] + 2 * n * e,
+                                      s->d_plane[1] + 2 * n * e, s->d_plane[2] + n * e, s->d_plane[3] + n * e,
+                                      cudaMemcpyHostToDevice, stream));
         s->on_device[e] = 1;
     }
     return INFMOE_OK;
@@ -306,15 +322,15 @@ int status_to_rc(int status) {
 }
 
 int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_offset, const int* d_slot_map,
-            int slots, float* const planes[6], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
-            float* g_lo, float* post, cudaStream_t stream) {
+            int slots, float* const planes[4], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
+            float* g_lo, float* post, cudaStream_t stream, cudaEvent_t mid = nullptr) {
     const bool umma = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);
     if (umma)
         return launch_ffn_umma(T, L->D, L->F, L->E, e_begin, e_end, d_offset, d_slot_map, slots, h_hi, h_lo, planes[0],
-                               planes[1], planes[2], planes[3], planes[4], planes[5], routed, g_hi, g_lo, post,
-                               L->d_status, L->num_sms, stream);
+                               planes[1], planes[2], planes[3], routed, g_hi, g_lo, post, L->d_status, L->num_sms,
+                               stream, mid);
     return launch_ffn_simt(T, L->D, L->F, e_begin, e_end, d_offset, d_slot_map, h_hi, h_lo, planes[0], planes[1],
-                           planes[2], planes[3], planes[4], planes[5], routed, g_hi, g_lo, post, stream);
+                           planes[2], planes[3], routed, g_hi, g_lo, post, stream);
 }
 
 void free_device_state(infmoe_layer* L) {
@@ -328,6 +344,7 @@ void free_device_state(infmoe_layer* L) {
     for (auto e : L->ev_ready) cudaEventDestroy(e);
     for (auto e : L->ev_freed) cudaEventDestroy(e);
     if (L->ev_fork) cudaEventDestroy(L->ev_fork);
+    for (auto e : L->prof_events) cudaEventDestroy(e);
     if (L->own_in) cudaFree(L->own_in);
     if (L->own_out) cudaFree(L->own_out);
     if (L->own_ws) cudaFree(L->own_ws);
@@ -352,6 +369,19 @@ std::shared_ptr<ExpertStore> make_store(int E, int D, int F) {
 int pinned_alloc(float** p, size_t elems) {
     if (*p) return INFMOE_OK;
     INFMOE_CUDA_TRY(cudaHostAlloc((void**)p, sizeof(float) * elems, cudaHostAllocDefault));
+    return INFMOE_OK;
+}
+
+constexpr int PROF_CALLS = 64;   // calls kept in the timing ring
+constexpr int PROF_MARKS = 7;    // start, route, dispatch, scatter, ffn gemm 1, ffn gemm 2, combine
+
+int prof_mark(infmoe_layer* L, int mark, cudaStream_t stream) {
+    if (!L->profiling) return INFMOE_OK;
+    if (L->prof_events.empty()) {
+        L->prof_events.resize((size_t)PROF_CALLS * PROF_MARKS);
+        for (auto& e : L->prof_events) INFMOE_CUDA_TRY(cudaEventCreate(&e));
+    }
+    INFMOE_CUDA_TRY(cudaEventRecord(L->prof_events[(size_t)(L->prof_calls % PROF_CALLS) * PROF_MARKS + mark], stream));
     return INFMOE_OK;
 }
 
@@ -523,10 +553,8 @@ int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const
         INFMOE_TRY(ensure_resident_planes(s));
         INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln + (size_t)e * s->D, ln_w, sizeof(float) * s->D, cudaMemcpyDeviceToDevice));
         s->ln_on_device[e] = 1;
-        const float* src[3] = {wi0, wi1, wo};
-        for (int m = 0; m < 3; ++m)
-            INFMOE_TRY(launch_split(src[m], s->d_plane[2 * m] + (size_t)e * n, s->d_plane[2 * m + 1] + (size_t)e * n, n,
-                                    0));
+        INFMOE_TRY(load_expert_planes(s->D, s->F, wi0, wi1, wo, s->d_plane[0] + 2 * n * e, s->d_plane[1] + 2 * n * e,
+                                      s->d_plane[2] + n * e, s->d_plane[3] + n * e, cudaMemcpyDeviceToDevice, 0));
         INFMOE_CUDA_TRY(cudaStreamSynchronize(0));
         s->on_device[e] = 1;
     } else {
@@ -624,11 +652,14 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
     L->last_count = count;
     L->last_offset = offset;
 
+    INFMOE_TRY(prof_mark(L, 0, stream));
     // 1. routing (plugin/MoELayerPlugin.cc:312-345)
     INFMOE_TRY(launch_route(d_in, L->d_centroids, L->flags.layernorm_before_score ? L->d_gating_ln : nullptr, T, L->D,
                             L->E, gate, score, L->d_status, stream));
+    INFMOE_TRY(prof_mark(L, 1, stream));
     // 2. dispatch metadata (:350-352)
     INFMOE_TRY(launch_dispatch(gate, T, L->E, pos, count, offset, L->d_status, stream));
+    INFMOE_TRY(prof_mark(L, 2, stream));
     if (L->identity) {
         // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
         INFMOE_TRY(launch_scatter(T, L->D, d_in, score, pos, routed, rscore, stream));
@@ -636,14 +667,21 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
         INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate, s->d_ln, routed, rscore, h_hi, h_lo, stream));
+        INFMOE_TRY(prof_mark(L, 3, stream));
         // 4. experts (:360-402)
         if (!streamed) {
+            cudaEvent_t mid = nullptr;
+            if (L->profiling) mid = L->prof_events[(size_t)(L->prof_calls % PROF_CALLS) * PROF_MARKS + 4];
             INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, nullptr, L->E, s->d_plane, h_hi, h_lo, routed, g_hi, g_lo, post,
-                               stream));
+                               stream, mid));
         } else {
             const size_t n = s->matrix_elems();
-            float* planes[6];
-            for (int p = 0; p < 6; ++p) planes[p] = (float*)(base + w.slots) + (size_t)p * L->mc * n;
+            // slot planes: w01_hi, w01_lo [mc][2F][D], then wo_hi, wo_lo [mc][D][F]
+            float* planes[4];
+            planes[0] = (float*)(base + w.slots);
+            planes[1] = planes[0] + 2 * n * L->mc;
+            planes[2] = planes[1] + 2 * n * L->mc;
+            planes[3] = planes[2] + n * L->mc;
             // the one host synchronisation of the streamed path: which experts have rows?
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_count, count, sizeof(int) * L->E, cudaMemcpyDeviceToHost, stream));
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
@@ -672,13 +710,9 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
                 cudaStream_t cs = L->copy_streams[j % L->copy_streams.size()];
                 // the slot is free once the expert that used it (j - mc) has run
                 if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
-                const float* src[3] = {s->h_wi0[e], s->h_wi1[e], s->h_wo[e]};
-                for (int m = 0; m < 3; ++m) {
-                    float* hi = planes[2 * m] + (size_t)slot * n;
-                    float* lo = planes[2 * m + 1] + (size_t)slot * n;
-                    INFMOE_CUDA_TRY(cudaMemcpyAsync(hi, src[m], sizeof(float) * n, cudaMemcpyHostToDevice, cs));
-                    INFMOE_TRY(launch_split(hi, hi, lo, n, cs));
-                }
+                INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e],
+                                              planes[0] + 2 * n * slot, planes[1] + 2 * n * slot, planes[2] + n * slot,
+                                              planes[3] + n * slot, cudaMemcpyHostToDevice, cs));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
                 INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
                 INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, L->mc, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
@@ -687,11 +721,14 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
             }
         }
     }
+    INFMOE_TRY(prof_mark(L, 5, stream));
     // 5. combine (:407-412; the gather reads the expert output)
     if (L->flags.base_layer_mix)
         INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, d_out, stream));
     else
         INFMOE_TRY(launch_gather(T, L->D, post, pos, d_out, stream));
+    INFMOE_TRY(prof_mark(L, 6, stream));
+    if (L->profiling) L->prof_calls++;
     return INFMOE_OK;
 }
 
@@ -757,6 +794,42 @@ int infmoe_layer_last_routing(const infmoe_layer* L, const int32_t** gate, const
     if (pos) *pos = L->last_pos;
     if (count) *count = L->last_count;
     if (offset) *offset = L->last_offset;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_set_profiling(infmoe_layer* L, int enable) {
+    if (!L) {
+        set_error("layer_set_profiling: null layer");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    L->profiling = enable != 0;
+    L->prof_calls = 0;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_stage_ms(infmoe_layer* L, float* ms, int32_t* calls) {
+    if (!L || !ms) {
+        set_error("layer_stage_ms: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    for (int i = 0; i < PROF_MARKS - 1; ++i) ms[i] = 0.f;
+    const int n = L->prof_calls < PROF_CALLS ? L->prof_calls : PROF_CALLS;
+    if (calls) *calls = n;
+    if (n == 0) return INFMOE_OK;
+    for (int c = 0; c < n; ++c) {
+        const cudaEvent_t* ev = &L->prof_events[(size_t)c * PROF_MARKS];
+        INFMOE_CUDA_TRY(cudaEventSynchronize(ev[PROF_MARKS - 1]));
+        for (int i = 0; i < PROF_MARKS - 1; ++i) {
+            float t = 0.f;
+            // when the experts are streamed the GEMMs are not split by a middle mark
+            if (cudaEventElapsedTime(&t, ev[i], ev[i + 1]) != cudaSuccess) {
+                cudaGetLastError();
+                t = 0.f;
+            }
+            ms[i] += t / (float)n;
+        }
+    }
+    L->prof_calls = 0;
     return INFMOE_OK;
 }
 
@@ -990,7 +1063,8 @@ int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* byte
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + 6 * align_up(4 * d * f) + 2 * ALIGN + ALIGN;
+    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + 2 * align_up(8 * d * f) + 2 * align_up(4 * d * f) +
+             2 * ALIGN + ALIGN;
     return INFMOE_OK;
 }
 
@@ -1019,16 +1093,19 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
     float* h_lo = (float*)take(4 * r * d);
     float* g_hi = (float*)take(4 * r * f);
     float* g_lo = (float*)take(4 * r * f);
-    float* planes[6];
-    for (auto& pl : planes) pl = (float*)take(4 * d * f);
+    float* planes[4];
+    planes[0] = (float*)take(8 * d * f);
+    planes[1] = (float*)take(8 * d * f);
+    planes[2] = (float*)take(4 * d * f);
+    planes[3] = (float*)take(4 * d * f);
     int* offset = (int*)take(8);
     int* status = (int*)take(4);
     const int h_offset[2] = {0, (int)rows};
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
-    const float* src[3] = {wi0, wi1, wo};
-    for (int m = 0; m < 3; ++m) INFMOE_TRY(launch_split(src[m], planes[2 * m], planes[2 * m + 1], d * f, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], planes[2], planes[3],
+                                  cudaMemcpyDeviceToDevice, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -1036,10 +1113,10 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
     const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
     if (simt)
         INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], planes[4], planes[5], x, g_hi, g_lo, y, stream));
+                                   planes[3], x, g_hi, g_lo, y, stream));
     else
         INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], planes[4], planes[5], x, g_hi, g_lo, y, status, sms, stream));
+                                   planes[3], x, g_hi, g_lo, y, status, sms, stream));
     int h_status = 0;
     INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));

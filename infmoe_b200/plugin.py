@@ -235,6 +235,18 @@ class MoELayer:
     def forward_host_ptr(self, h_in: int, h_out: int, token_num: int) -> None:
         capi.check(capi.lib().infmoe_layer_forward_host(self._h, h_in, h_out, int(token_num)))
 
+    def set_profiling(self, enable: bool) -> None:
+        capi.check(capi.lib().infmoe_layer_set_profiling(self._h, 1 if enable else 0))
+
+    STAGES = ("route", "dispatch", "scatter", "ffn_gemm1", "ffn_gemm2", "combine")
+
+    def stage_ms(self):
+        """Average device milliseconds per stage over the calls since the last read -> (dict, calls)."""
+        ms = (ctypes.c_float * 6)()
+        n = ctypes.c_int32()
+        capi.check(capi.lib().infmoe_layer_stage_ms(self._h, ms, ctypes.byref(n)))
+        return dict(zip(self.STAGES, [float(v) for v in ms])), int(n.value)
+
     def last_routing(self):
         """Device pointers (gate, score, pos, count, offset) of the last enqueue."""
         ptrs = [ctypes.c_void_p() for _ in range(5)]
