@@ -48,6 +48,8 @@
 // copies in flight land, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace infmoe {
@@ -549,15 +551,33 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a1.out_lo = g_lo;
     a1.resid = nullptr;
     a1.status = status;
-    INFMOE_TRY((launch_one<EPI_GELU_PAIR, 16, 192, 5>(a1, T, slots, w01_hi, w01_lo, h_hi, h_lo, num_sms, stream)));
-    if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));
     GemmArgs a2 = a1;
     a2.M_total = D;
     a2.K = F;
     a2.out_hi = post;
     a2.out_lo = nullptr;
     a2.resid = routed;
-    INFMOE_TRY((launch_one<EPI_RESIDUAL, 16, 192, 5>(a2, T, slots, wo_hi, wo_lo, g_hi, g_lo, num_sms, stream)));
+    // Tile shape: k block (floats), token chunk, pipeline depth.  INFMOE_GEMM_TILE selects another
+    // instantiation for tuning runs.
+    static const int variant = [] {
+        const char* v = getenv("INFMOE_GEMM_TILE");
+        return v ? atoi(v) : 0;
+    }();
+#define INFMOE_LAUNCH_PAIR(BK, NMAX, STAGES)                                                                        \
+    do {                                                                                                             \
+        INFMOE_TRY((launch_one<EPI_GELU_PAIR, BK, NMAX, STAGES>(a1, T, slots, w01_hi, w01_lo, h_hi, h_lo, num_sms,    \
+                                                                stream)));                                           \
+        if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));                                          \
+        INFMOE_TRY((launch_one<EPI_RESIDUAL, BK, NMAX, STAGES>(a2, T, slots, wo_hi, wo_lo, g_hi, g_lo, num_sms,       \
+                                                               stream)));                                            \
+    } while (0)
+    switch (variant) {
+        case 1: INFMOE_LAUNCH_PAIR(32, 192, 2); break;
+        case 2: INFMOE_LAUNCH_PAIR(32, 160, 3); break;
+        case 3: INFMOE_LAUNCH_PAIR(16, 256, 4); break;
+        default: INFMOE_LAUNCH_PAIR(16, 192, 5); break;
+    }
+#undef INFMOE_LAUNCH_PAIR
     return INFMOE_OK;
 }
 

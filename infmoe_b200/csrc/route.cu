@@ -6,11 +6,13 @@
 //   cublasSgemm_v2       plugin/MoELayerPlugin.cc:334-336  (aff = Xs * C^T)
 //   moe_expert_select    plugin/cuda/moe.cu:147-159     (strict '>' scan, first maximum wins)
 //
-// Layout: X [T][D], centroids [E][D], both row-major FP32.  A warp owns TPW
-// tokens at once and, for a group of EG experts at a time, keeps TPW*EG
-// per-lane partial sums in registers; every centroid fragment loaded is used
-// for TPW tokens.  The per-(token, expert) summation order does not depend on
-// the blocking, so the result is the canonical order of common.cuh bit for bit.
+// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA of 8 warps owns
+// 32 tokens (TPW = 4 per warp).  Centroids are streamed through shared memory in
+// tiles of EG experts x KT floats with double-buffered cp.async, so every
+// centroid byte is fetched from L2 once per CTA and every LDS.128 feeds
+// 4 * TPW fused multiply-adds; a warp keeps TPW * EG per-lane partial sums in
+// registers.  The per-(token, expert) summation order does not depend on the
+// blocking, so the result is the canonical order of common.cuh bit for bit.
 // All arithmetic is explicit round-to-nearest FP32 (no tensor cores).
 #include "common.cuh"
 
@@ -19,16 +21,45 @@ namespace infmoe {
 namespace {
 
 constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
 
-template <int TPW, int EG>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Fills one shared-memory tile: experts [e0, e0+EG) x floats [k0, k0+KT) of the centroids, zero padded.
+template <int EG, int KT>
+__device__ __forceinline__ void load_centroid_tile(float* __restrict__ tile, const float* __restrict__ C, int E, int D,
+                                                   int e0, int k0, bool vec) {
+    if (vec) {
+        for (int idx = threadIdx.x; idx < EG * (KT / 4); idx += ROUTE_THREADS) {
+            const int j = idx / (KT / 4), k = (idx % (KT / 4)) * 4;
+            float* dst = tile + j * KT + k;
+            if (e0 + j < E && k0 + k < D) cp_async16(dst, C + (long long)(e0 + j) * D + k0 + k);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < EG * KT; idx += ROUTE_THREADS) {
+            const int j = idx / KT, k = idx % KT;
+            tile[idx] = (e0 + j < E && k0 + k < D) ? C[(long long)(e0 + j) * D + k0 + k] : 0.f;
+        }
+    }
+}
+
+template <int TPW, int EG, int KT>
+__global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
              long long T, int D, int E, int vec, int* __restrict__ gate, float* __restrict__ score,
              int* __restrict__ status) {
+    extern __shared__ __align__(16) float s_tiles[];   // [2][EG][KT]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const long long t0 = ((long long)blockIdx.x * ROUTE_WARPS + warp) * TPW;
-    if (t0 >= T) return;
+    const bool warp_live = t0 < T;   // whole warps past the end still help loading tiles
 
     const float* rows[TPW];
     float mean[TPW], rstd[TPW];
@@ -36,12 +67,12 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {
         live[i] = t0 + i < T;
-        rows[i] = X + (live[i] ? (t0 + i) : t0) * (long long)D;  // dead slots alias the first row
+        rows[i] = X + (live[i] ? (t0 + i) : (warp_live ? t0 : 0)) * (long long)D;  // dead slots alias a valid row
         mean[i] = 0.f;
         rstd[i] = 1.f;
     }
     const bool use_ln = gamma != nullptr;
-    if (use_ln) {
+    if (use_ln && warp_live) {
 #pragma unroll
         for (int i = 0; i < TPW; ++i) warp_row_stats(rows[i], D, vec != 0, mean[i], rstd[i]);
     }
@@ -54,6 +85,7 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         best_e[i] = -1;
     }
 
+    const int ntiles = (D + KT - 1) / KT;
     for (int e0 = 0; e0 < E; e0 += EG) {
         float acc[TPW][EG];
 #pragma unroll
@@ -61,37 +93,53 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
 #pragma unroll
             for (int j = 0; j < EG; ++j) acc[i][j] = 0.f;
 
-        for (int base = 4 * lane; base < D; base += 128) {
-            float xs[TPW][4];
-            float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (use_ln) g4 = load_row4(gamma, base, D, vec != 0);
+        load_centroid_tile<EG, KT>(s_tiles, C, E, D, e0, 0, vec != 0);
+        cp_async_commit();
+        for (int kt = 0; kt < ntiles; ++kt) {
+            const float* tile = s_tiles + (kt & 1) * EG * KT;
+            if (kt + 1 < ntiles)
+                load_centroid_tile<EG, KT>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT, vec != 0);
+            cp_async_commit();
+            cp_async_wait<1>();   // tile kt has landed (the group of tile kt+1 may still be in flight)
+            __syncthreads();
+            if (warp_live) {
 #pragma unroll
-            for (int i = 0; i < TPW; ++i) {
-                const float4 v = load_row4(rows[i], base, D, vec != 0);
-                if (use_ln) {
-                    xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g4.x);
-                    xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g4.y);
-                    xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g4.z);
-                    xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g4.w);
-                } else {
-                    xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
-                }
-            }
-            const int nvalid = min(4, D - base);
+                for (int it = 0; it < KT / 128; ++it) {
+                    const int kl = it * 128 + 4 * lane;       // offset inside the tile
+                    const int base = kt * KT + kl;            // offset inside the row
+                    if (base < D) {
+                        float xs[TPW][4];
+                        float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (use_ln) g4 = load_row4(gamma, base, D, vec != 0);
 #pragma unroll
-            for (int j = 0; j < EG; ++j) {
-                if (e0 + j < E) {
-                    const float4 c = load_row4(C + (long long)(e0 + j) * D, base, D, vec != 0);
-                    const float cc[4] = {c.x, c.y, c.z, c.w};
+                        for (int i = 0; i < TPW; ++i) {
+                            const float4 v = load_row4(rows[i], base, D, vec != 0);
+                            if (use_ln) {
+                                xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g4.x);
+                                xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g4.y);
+                                xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g4.z);
+                                xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g4.w);
+                            } else {
+                                xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
+                            }
+                        }
+                        const int nvalid = min(4, D - base);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if (k < nvalid) {
+                        for (int j = 0; j < EG; ++j) {
+                            const float4 c = *reinterpret_cast<const float4*>(tile + j * KT + kl);
+                            const float cc[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
-                            for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
+                            for (int k = 0; k < 4; ++k) {
+                                if (k < nvalid) {
+#pragma unroll
+                                    for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
+                                }
+                            }
                         }
                     }
                 }
             }
+            __syncthreads();   // everyone is done with tile kt before it is overwritten
         }
 #pragma unroll
         for (int j = 0; j < EG; ++j) {
@@ -107,7 +155,7 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
             }
         }
     }
-    if (lane == 0) {
+    if (lane == 0 && warp_live) {
 #pragma unroll
         for (int i = 0; i < TPW; ++i) {
             if (!live[i]) continue;
@@ -163,11 +211,13 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
     }
     if (T == 0) return INFMOE_OK;
     const bool vec = (D % 4 == 0) && (((uintptr_t)X | (uintptr_t)C | (uintptr_t)gamma) % 16 == 0);
-    constexpr int TPW = 4, EG = 16;
+    constexpr int TPW = 4, EG = 16, KT = 512;
+    constexpr int SMEM = 2 * EG * KT * (int)sizeof(float);
     const long long tokens_per_cta = (long long)ROUTE_WARPS * TPW;
     const long long grid = (T + tokens_per_cta - 1) / tokens_per_cta;
-    route_kernel<TPW, EG><<<(unsigned)grid, ROUTE_WARPS * 32, 0, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate,
-                                                                          score, status);
+    auto kern = route_kernel<TPW, EG, KT>;
+    INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    kern<<<(unsigned)grid, ROUTE_THREADS, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
