@@ -573,9 +573,9 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     } while (0)
     switch (variant) {
         case 1: INFMOE_LAUNCH_PAIR(32, 192, 2); break;
-        case 2: INFMOE_LAUNCH_PAIR(32, 160, 3); break;
+        case 2: INFMOE_LAUNCH_PAIR(16, 192, 5); break;
         case 3: INFMOE_LAUNCH_PAIR(16, 256, 4); break;
-        default: INFMOE_LAUNCH_PAIR(16, 192, 5); break;
+        default: INFMOE_LAUNCH_PAIR(32, 160, 3); break;   // 128-byte rows: fewest TMA requests per byte
     }
 #undef INFMOE_LAUNCH_PAIR
     return INFMOE_OK;
