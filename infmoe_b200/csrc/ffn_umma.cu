@@ -118,6 +118,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Brings a weight box into L2 without touching shared memory.
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -202,6 +208,7 @@ struct GemmArgs {
     float* out_lo;              // GELU_PAIR: g_lo
     const float* resid;         // RESIDUAL: x [T][M_total]
     int* status;
+    int prefetch;               // L2 prefetch distance of the weight stream, in k blocks
 };
 
 struct TileInfo {
@@ -306,14 +313,42 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
 
     if (warp == 0) {
         // ================= TMA producer =================
+        // Optional L2 prefetch cursor PF k blocks ahead of the loads (INFMOE_GEMM_PREFETCH).  Measured
+        // on B200 it does not help this kernel (the weight stream already runs at ~75% of the copy
+        // bandwidth; distances >= 8 k blocks thrash L2), so it is off by default.
         if (lane == 0) {
+            const int PF = args.prefetch;    // look-ahead in k blocks
             uint32_t it = 0;
+            int la_tile = blockIdx.x, la_kb = 0, la_m0 = 0, la_slot = 0;
+            bool la_valid = la_tile < total_tiles;
+            if (la_valid) {
+                const TileInfo t = decode_tile<NMAX>(la_tile, s_prefix, args);
+                la_m0 = t.mb * UMMA_M;
+                la_slot = t.slot;
+            }
+            auto prefetch_next = [&]() {
+                if (!la_valid) return;
+                tma_prefetch_3d(&map_w_hi, la_kb * BK, la_m0, la_slot);
+                tma_prefetch_3d(&map_w_lo, la_kb * BK, la_m0, la_slot);
+                if (++la_kb == KB) {
+                    la_kb = 0;
+                    la_tile += gridDim.x;
+                    la_valid = la_tile < total_tiles;
+                    if (la_valid) {
+                        const TileInfo t = decode_tile<NMAX>(la_tile, s_prefix, args);
+                        la_m0 = t.mb * UMMA_M;
+                        la_slot = t.slot;
+                    }
+                }
+            };
+            for (int i = 0; i < PF; ++i) prefetch_next();
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
                 const int nbox = (t.n_pad + 31) >> 5;
                 const uint32_t bytes = 2 * C::W_TILE + 2 * nbox * 32 * BK * 4;
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
+                    prefetch_next();
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
@@ -551,6 +586,11 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a1.out_lo = g_lo;
     a1.resid = nullptr;
     a1.status = status;
+    static const int prefetch = [] {
+        const char* v = getenv("INFMOE_GEMM_PREFETCH");
+        return v ? atoi(v) : 0;
+    }();
+    a1.prefetch = prefetch;
     GemmArgs a2 = a1;
     a2.M_total = D;
     a2.K = F;
