@@ -197,6 +197,30 @@ INFMOE_API int infmoe_t5ff_run(int64_t rows, int32_t embedding_size, int32_t hid
                                const float* d_wi0, const float* d_wi1, const float* d_wo, const float* d_x,
                                float* d_y, void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* The same expert FFN for callers that cannot allocate device memory -- a TensorRT
+ * plugin inside enqueue(), code that runs while a CUDA graph is being captured, a
+ * serving loop that may not risk the device-wide synchronisation of cudaMalloc.
+ * It has no counterpart in the reference: it is infmoe_t5ff_run without the
+ * workspace argument.  All scratch lives in an array that is part of the library
+ * image (32 MiB, held by every GPU that loads the library until the process
+ * exits); the call performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine.
+ *   - Sizes whose scratch need (infmoe_t5ff_workspace_bytes) exceeds the array are
+ *     rejected with INFMOE_ERR_UNSUPPORTED; infmoe_t5ff_static_limit reports both
+ *     numbers.  Examples that fit: d_model 512, d_ff 1024, 256 rows; d_model 1024,
+ *     d_ff 1024, 64 rows.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current).  Make that first call before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents;
+ *     the function rewrites everything it reads and clears its status word, so
+ *     back-to-back calls on one stream are fine, but two calls that overlap on
+ *     the GPU (different streams, or different host threads) race on it. */
+INFMOE_API int infmoe_t5ff_static_limit(int64_t rows, int32_t embedding_size, int32_t hidden_size, size_t* needed,
+                                        size_t* available);
+INFMOE_API int infmoe_t5ff_run_static(int64_t rows, int32_t embedding_size, int32_t hidden_size,
+                                      const float* d_ln_w, const float* d_wi0, const float* d_wi1,
+                                      const float* d_wo, const float* d_x, float* d_y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

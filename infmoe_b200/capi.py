@@ -83,6 +83,8 @@ SIGNATURES = {
     "infmoe_gelu_dot": [_vp, _vp, _sz, _vp],
     "infmoe_t5ff_workspace_bytes": [_i64, _i32, _i32, ctypes.POINTER(_sz)],
     "infmoe_t5ff_run": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],
+    "infmoe_t5ff_static_limit": [_i64, _i32, _i32, ctypes.POINTER(_sz), ctypes.POINTER(_sz)],
+    "infmoe_t5ff_run_static": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "infmoe_last_error": [],
 }
 _RESTYPES = {"infmoe_last_error": ctypes.c_char_p, "infmoe_layer_kernel_launches": ctypes.c_int64}

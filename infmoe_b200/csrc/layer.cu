@@ -1124,3 +1124,122 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
 }
 
 }  // extern "C"
+
+// =================================================================================================
+// Expert FFN for callers that must not allocate
+// =================================================================================================
+// A TensorRT plugin's enqueue(), code running while a CUDA graph is being captured, and serving
+// loops with a hard latency budget may not call cudaMalloc: the call can synchronise the whole
+// device, is refused during capture, and would break an engine whose memory plan was fixed when
+// it was built.  infmoe_t5ff_run needs a caller-provided workspace, which such a caller has to
+// have planned for in advance.  infmoe_t5ff_run_static needs none: its scratch (LayerNorm output,
+// gate activations, the TF32 head/tail copies of the three weight matrices) lives in the array
+// below, which is part of the library image.  Every GPU that loads the library keeps these
+// INFMOE_STATIC_SCRATCH_BYTES resident until the process exits, so the size is deliberately modest;
+// larger problems are rejected and belong to infmoe_t5ff_run.
+#define INFMOE_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[INFMOE_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[MAX_DEVICES] = {};   // device address of g_static_scratch, per device
+
+// In host code `g_static_scratch` is only a handle for the symbol, not an address a kernel can
+// use; the device address has to be asked for, once per device, with that device current.
+int static_scratch_address(unsigned char** out) {
+    int dev = -1;
+    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) {
+        set_error("t5ff_run_static: device index %d out of range", dev);
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        INFMOE_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) {
+            set_error("t5ff_run_static: cudaGetSymbolAddress returned a null address");
+            return INFMOE_ERR_CUDA;
+        }
+        g_static_ptr[dev] = (unsigned char*)p;
+    }
+    *out = g_static_ptr[dev];
+    return INFMOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int infmoe_t5ff_static_limit(int64_t rows, int32_t D, int32_t F, size_t* needed, size_t* available) {
+    size_t need = 0;
+    INFMOE_TRY(infmoe_t5ff_workspace_bytes(rows, D, F, &need));
+    if (needed) *needed = need;
+    if (available) *available = (size_t)INFMOE_STATIC_SCRATCH_BYTES;
+    return INFMOE_OK;
+}
+
+int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w, const float* wi0, const float* wi1,
+                           const float* wo, const float* x, float* y, void* stream_v) {
+    if (rows < 0 || D <= 0 || F <= 0 || !ln_w || !wi0 || !wi1 || !wo || (rows > 0 && (!x || !y))) {
+        set_error("t5ff_run_static: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0) return INFMOE_OK;
+    size_t need = 0;
+    INFMOE_TRY(infmoe_t5ff_workspace_bytes(rows, D, F, &need));
+    if (need > (size_t)INFMOE_STATIC_SCRATCH_BYTES) {
+        set_error("t5ff_run_static: rows=%lld d_model=%d d_ff=%d needs %zu bytes of scratch but the built-in array "
+                  "holds %u; use infmoe_t5ff_run with a workspace of your own", (long long)rows, D, F, need,
+                  INFMOE_STATIC_SCRATCH_BYTES);
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    unsigned char* scratch = nullptr;
+    INFMOE_TRY(static_scratch_address(&scratch));
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
+    char* p = (char*)scratch;   // the array is 256-byte aligned already
+    auto take = [&](size_t bytes) {
+        char* at = p;
+        p += align_up(bytes);
+        return at;
+    };
+    float* h_hi = (float*)take(4 * r * d);
+    float* h_lo = (float*)take(4 * r * d);
+    float* g_hi = (float*)take(4 * r * f);
+    float* g_lo = (float*)take(4 * r * f);
+    float* planes[4];
+    planes[0] = (float*)take(8 * d * f);
+    planes[1] = (float*)take(8 * d * f);
+    planes[2] = (float*)take(4 * d * f);
+    planes[3] = (float*)take(4 * d * f);
+    int* offset = (int*)take(8);
+    int* status = (int*)take(4);
+    // The array keeps whatever the previous call left: everything read below is rewritten first
+    // (offsets, both activation planes, all weight planes); only the status word must start at zero.
+    const int h_offset[2] = {0, (int)rows};
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], planes[2], planes[3],
+                                  cudaMemcpyDeviceToDevice, stream));
+    int dev = 0, sms = 0;
+    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
+    INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const char* path = getenv("INFMOE_FFN");
+    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
+    if (simt)
+        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], planes[2],
+                                   planes[3], x, g_hi, g_lo, y, stream));
+    else
+        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], planes[2],
+                                   planes[3], x, g_hi, g_lo, y, status, sms, stream));
+    int h_status = 0;
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+    return status_to_rc(h_status);
+}
+
+}  // extern "C"
