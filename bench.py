@@ -122,7 +122,7 @@ def cpu_step(oracle, ws, x, cent, ln, experts):
     return time.perf_counter() - t0
 
 
-def run_reference_arm(args, w):
+def run_reference_arm(args, w, scaling="weak"):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -137,7 +137,7 @@ def run_reference_arm(args, w):
               f"weights in host memory")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(w, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
@@ -149,9 +149,9 @@ def run_reference_arm(args, w):
 
 
 def workload_config(w, n_gpus):
-    return {"workload": w.name, "moe_variant": w.variant, "expert_count": w.expert_count * (n_gpus if n_gpus > 1 else 1),
+    return {"workload": w.name, "moe_variant": w.variant, "expert_count": w.expert_count,
             "d_model": w.embedding_size, "d_ff": w.hidden_size,
-            "tokens": w.tokens * (n_gpus if n_gpus > 1 else 1), "experts": "streamed" if w.streamed else "resident",
+            "tokens": w.tokens, "experts": "streamed" if w.streamed else "resident",
             "parallelism": f"ep{n_gpus}" if n_gpus > 1 else "single",
             "l2": "expert weights (GBs) stream through L2 every step; nothing is flushed explicitly"}
 
@@ -282,23 +282,30 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    name = args.workload or ("cpm2" if args.gpus == 1 else "ep_cpm2")
-    w = synth.WORKLOADS[name]
+    w, scaling = resolve_workload(args)
     if args.impl == "reference":
-        if args.gpus > 1:
-            w = ep_local_workload(w, args.gpus)
-        run_reference_arm(args, w)
+        run_reference_arm(args, w, scaling)
         return
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_single(args, w)
     else:
         from infmoe_b200 import ep_bench
-        ep_bench.run(args, w, METRIC, UNIT, ClockSampler, _peaks, workload_config)
+        ep_bench.run(args, w, scaling, METRIC, UNIT, ClockSampler, _peaks, workload_config)
 
 
-def ep_local_workload(w, n):
-    """Per-rank share of the expert-parallel workload (weak scaling: fixed per-GPU work)."""
-    return w
+def resolve_workload(args):
+    """-> (whole-job workload, "weak" | "strong").
+
+    One GPU: the named workload (default cpm2).  N GPUs: by default N copies of that per-GPU share (32 N experts,
+    4096 N tokens: weak scaling, and N = 1 is the single-GPU workload itself); `--workload ep_cpm2` is the
+    fixed-size expert-parallel case (E = 128, 65536 tokens in total) sharded over the ranks."""
+    n = max(args.gpus, int(os.environ.get("WORLD_SIZE", "1")))
+    if n == 1:
+        return synth.WORKLOADS[args.workload or "cpm2"], "weak"
+    if args.workload == "ep_cpm2":
+        return synth.WORKLOADS["ep_cpm2"], "strong"
+    base = synth.WORKLOADS[args.workload or "cpm2"]
+    return synth.scaled(base, expert_count=base.expert_count * n, batch=base.batch * n), "weak"
 
 
 if __name__ == "__main__":

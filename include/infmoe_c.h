@@ -99,6 +99,15 @@ INFMOE_API int infmoe_layer_workspace_bytes(const infmoe_layer* layer, int64_t t
 INFMOE_API int infmoe_layer_enqueue(infmoe_layer* layer, const float* d_input, float* d_output, void* d_workspace,
                                     size_t workspace_bytes, int64_t token_num, void* stream);
 
+/* The experts alone, for rows whose expert is already known: d_y[i,:] = expert d_expert_of_row[i] applied to
+ * d_rows[i,:] (T5FFLayer::run, plugin/sublayers/T5FFLayer.cc:90-141, grouped over all experts of this layer).
+ * Rows may come in any order; results come back in the same order; no routing and no score mix.  This is what an
+ * expert-parallel rank runs on the rows it received from the other ranks (the reference has no multi-GPU path).
+ * Workspace as for infmoe_layer_enqueue with token_num = rows. */
+INFMOE_API int infmoe_layer_expert_forward(infmoe_layer* layer, const float* d_rows, const int32_t* d_expert_of_row,
+                                           float* d_y, void* d_workspace, size_t workspace_bytes, int64_t rows,
+                                           void* stream);
+
 /* Blocks until `stream` is idle and returns the device-side status of the calls enqueued so far. */
 INFMOE_API int infmoe_layer_sync_status(infmoe_layer* layer, void* stream);
 

@@ -594,8 +594,12 @@ int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes
     return INFMOE_OK;
 }
 
-int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
-                         void* stream_v) {
+// The forward pass.  With given_gate == nullptr this is the whole layer (routing included).  With a
+// caller-provided expert index per row it runs dispatch + experts only and returns every row's expert
+// output in the caller's row order (no score mix): the building block of the expert-parallel path, where
+// routing happened on the rank that owns the token.
+static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
+                     void* stream_v, const int* given_gate) {
     if (!L || T < 0 || (T > 0 && (!d_in || !d_out || !d_ws))) {
         set_error("layer_enqueue: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
@@ -646,7 +650,9 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
     float* h_lo = (float*)(base + w.h_lo);
     float* g_hi = (float*)(base + w.g_hi);
     float* g_lo = (float*)(base + w.g_lo);
-    L->last_gate = gate;
+    const int* gate_in = given_gate ? given_gate : gate;
+    if (given_gate) score = nullptr;
+    L->last_gate = gate_in;
     L->last_score = score;
     L->last_pos = pos;
     L->last_count = count;
@@ -654,11 +660,12 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
 
     INFMOE_TRY(prof_mark(L, 0, stream));
     // 1. routing (plugin/MoELayerPlugin.cc:312-345)
-    INFMOE_TRY(launch_route(d_in, L->d_centroids, L->flags.layernorm_before_score ? L->d_gating_ln : nullptr, T, L->D,
-                            L->E, gate, score, L->d_status, stream));
+    if (!given_gate)
+        INFMOE_TRY(launch_route(d_in, L->d_centroids, L->flags.layernorm_before_score ? L->d_gating_ln : nullptr, T,
+                                L->D, L->E, gate, score, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 1, stream));
     // 2. dispatch metadata (:350-352)
-    INFMOE_TRY(launch_dispatch(gate, T, L->E, pos, count, offset, L->d_status, stream));
+    INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 2, stream));
     if (L->identity) {
         // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
@@ -666,7 +673,8 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
         INFMOE_CUDA_TRY(cudaMemcpyAsync(post, routed, sizeof(float) * (size_t)T * L->D, cudaMemcpyDeviceToDevice, stream));
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
-        INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate, s->d_ln, routed, rscore, h_hi, h_lo, stream));
+        INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate_in, s->d_ln, routed, rscore, h_hi, h_lo,
+                                           stream));
         INFMOE_TRY(prof_mark(L, 3, stream));
         // 4. experts (:360-402)
         if (!streamed) {
@@ -723,13 +731,28 @@ int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void*
     }
     INFMOE_TRY(prof_mark(L, 5, stream));
     // 5. combine (:407-412; the gather reads the expert output)
-    if (L->flags.base_layer_mix)
+    if (L->flags.base_layer_mix && !given_gate)
         INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, d_out, stream));
     else
         INFMOE_TRY(launch_gather(T, L->D, post, pos, d_out, stream));
     INFMOE_TRY(prof_mark(L, 6, stream));
     if (L->profiling) L->prof_calls++;
     return INFMOE_OK;
+}
+
+int infmoe_layer_enqueue(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
+                         void* stream_v) {
+    return layer_run(L, d_in, d_out, d_ws, ws_bytes, T, stream_v, nullptr);
+}
+
+int infmoe_layer_expert_forward(infmoe_layer* L, const float* d_rows, const int32_t* d_expert_of_row, float* d_out,
+                                void* d_ws, size_t ws_bytes, int64_t rows, void* stream_v) {
+    if (rows > 0 && !d_expert_of_row) {
+        set_error("layer_expert_forward: expert index array is required");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0) return INFMOE_OK;
+    return layer_run(L, d_rows, d_out, d_ws, ws_bytes, rows, stream_v, d_expert_of_row);
 }
 
 int infmoe_layer_sync_status(infmoe_layer* L, void* stream_v) {

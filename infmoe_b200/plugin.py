@@ -131,6 +131,23 @@ class MoELayer:
                                                    int(token_num), stream))
         return 0
 
+    def expert_forward(self, rows, expert_of_row, out=None, stream: Optional[int] = None):
+        """Runs only the experts on CUDA tensor `rows` [n][D] whose expert indices (int32 [n]) are known."""
+        import torch
+
+        n = rows.shape[0]
+        if out is None:
+            out = torch.empty_like(rows)
+        if n == 0:
+            return out
+        need = self.get_workspace_size(n)
+        if self._ws is None or self._ws.numel() < need or self._ws.device != rows.device:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=rows.device)
+        s = torch.cuda.current_stream(rows.device).cuda_stream if stream is None else stream
+        capi.check(capi.lib().infmoe_layer_expert_forward(self._h, rows.data_ptr(), expert_of_row.data_ptr(),
+                                                          out.data_ptr(), self._ws.data_ptr(), self._ws.numel(), n, s))
+        return out
+
     def sync_status(self, stream: int = 0) -> None:
         capi.check(capi.lib().infmoe_layer_sync_status(self._h, stream))
 
