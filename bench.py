@@ -235,8 +235,12 @@ def run_single(args, w):
     if g1_ms:
         achieved = useful_flops / (g1_ms * 1e-3) / 1e12
         weight_bytes = 2.0 * (2 * D * F * 4) * active  # head + tail planes of the interleaved wi_0/wi_1 matrix
+        # DRAM bytes per launch from the ncu capture of workload cpm2_profile (profiles/): 2.778 GB for 8 experts x
+        # 10240 interleaved weight rows x 4096 floats = 8.28 bytes per weight element (8 algorithmic), scaled by
+        # the weight elements this launch streams.
+        traffic = 8.28 * active * 2.0 * F * D if not w.streamed else None
         roofline = {"kernel": "ffn_umma_kernel<EPI_GELU_PAIR>", "bound": "tensor", "achieved": achieved,
-                    "peak": peak_3xtf32, "unit": "TFLOP/s", "frac": achieved / peak_3xtf32, "traffic": None,
+                    "peak": peak_3xtf32, "unit": "TFLOP/s", "frac": achieved / peak_3xtf32, "traffic": traffic,
                     "peak_source": f"bf16 sustained {peaks['bf16_sustained']} TFLOP/s of {peaks['source']} / 6 "
                                    "(TF32 = bf16/2, 3 MMAs per product)",
                     "ms": g1_ms, "weight_stream_gbs": weight_bytes / (g1_ms * 1e-3) / 1e9,

@@ -1,0 +1,96 @@
+"""Parity at the benchmark's full sizes, where the FP64 oracle cannot evaluate everything: routing and dispatch
+are still compared bit for bit on every token; the layer output is checked on sampled rows of sampled experts
+against the FP64 oracle, and through size-independent properties (token-permutation equivariance, determinism,
+scatter/gather identity)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+def _build(w, torch):
+    from infmoe_b200 import MoELayer, synth
+    x, c, ln = synth.gen_inputs(w)
+    layer = MoELayer.create(w.expert_count, w.embedding_size, w.hidden_size, 2, c, None, "T5_FF", w.variant, ln)
+    for e in range(w.expert_count):
+        layer.set_expert(e, *synth.gen_expert_torch(w, e, torch.device("cuda")))
+    layer.set_residency(1)
+    return layer, x, c, ln
+
+
+def _check_full(name, oracle, sample_experts, rows_per_expert):
+    import torch
+    from infmoe_b200 import synth
+    from infmoe_b200.devmem import read_device
+    assert torch.cuda.is_available()
+    w = synth.WORKLOADS[name]
+    layer, x, c, ln = _build(w, torch)
+    dx = torch.from_numpy(x).cuda()
+    out = layer.forward(dx)
+    layer.sync_status()
+    T, E = w.tokens, w.expert_count
+    gate_p, score_p, pos_p, count_p, offset_p = layer.last_routing()
+    gate, score = read_device(gate_p, T, np.int32), read_device(score_p, T, np.float32)
+    pos, count, offset = read_device(pos_p, T, np.int32), read_device(count_p, E, np.int32), read_device(offset_p, E + 1, np.int32)
+    ogate, oscore = oracle.route(x, c, ln if w.variant == "cpm_2" else None)
+    np.testing.assert_array_equal(gate, ogate)
+    np.testing.assert_array_equal(score.view(np.uint32), oscore.view(np.uint32))
+    oc, oo, op = oracle.dispatch(ogate, E)
+    np.testing.assert_array_equal(count, oc)
+    np.testing.assert_array_equal(offset, oo)
+    np.testing.assert_array_equal(pos, op)
+    out_h = out.cpu().numpy()
+    assert np.isfinite(out_h).all()
+    # sampled rows of sampled experts against the FP64 oracle
+    rng = np.random.default_rng(0)
+    busiest = np.argsort(-oc)
+    chosen = list(busiest[:1]) + list(rng.choice(busiest[1:], size=sample_experts - 1, replace=False))
+    for e in chosen:
+        rows = op[oo[e]:oo[e + 1]]
+        if rows.size == 0:
+            continue
+        rows = rng.choice(rows, size=min(rows_per_expert, rows.size), replace=False)
+        ws = [t.cpu().numpy() for t in synth.gen_expert_torch(w, int(e), torch.device("cuda"))]
+        y64 = oracle.expert_ffn_f64(x[rows], *ws)
+        if w.variant == "base_layer":
+            alpha = 1.0 / (1.0 + np.exp(-oscore[rows].astype(np.float64)))[:, None]
+            y64 = alpha * y64 + (1 - alpha) * x[rows]
+        err = oracle.rel_l2(out_h[rows], y64)
+        assert err <= TOL, (int(e), err)
+        assert oracle.rel_l2(out_h[rows] - x[rows], y64 - x[rows]) <= 10 * TOL
+    # equivariance: permuting the tokens permutes the output rows, bit for bit
+    perm = rng.permutation(T)
+    out_p = layer.forward(torch.from_numpy(x[perm]).cuda())
+    layer.sync_status()
+    np.testing.assert_array_equal(out_p.cpu().numpy(), out_h[perm])
+    # determinism
+    np.testing.assert_array_equal(layer.forward(dx).cpu().numpy(), out_h)
+    layer.terminate()
+    return oc
+
+
+def test_cpm2_full_size(oracle):
+    count = _check_full("cpm2", oracle, sample_experts=3, rows_per_expert=6)
+    assert count.min() > 0 and count.max() < 200          # near-uniform routing, as the workload intends
+
+
+def test_base_layer_zipf_full_size(oracle):
+    count = _check_full("base_layer_zipf", oracle, sample_experts=4, rows_per_expert=8)
+    assert count.max() > 10 * np.median(count)            # the skew is real: a few experts take most tokens
+
+
+def test_identity_full_size_roundtrip():
+    """Scatter then gather over 65536 x 4096 floats is the identity (the Identity sublayer)."""
+    import torch
+    from infmoe_b200 import MoELayer
+    assert torch.cuda.is_available()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(65536, 4096, generator=g, device="cuda")
+    c = torch.randn(128, 4096, generator=g, device="cuda").cpu().numpy()
+    layer = MoELayer.create(128, 4096, 64, 2, c, None, "Identity", "default", None)
+    out = layer.forward(x)
+    layer.sync_status()
+    assert torch.equal(out, x)
+    layer.terminate()
