@@ -727,6 +727,7 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                                    stream));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[slot], stream));
             }
+            INFMOE_TRY(prof_mark(L, 4, stream));   // streamed: copies and both GEMMs are timed together
         }
     }
     INFMOE_TRY(prof_mark(L, 5, stream));
