@@ -178,6 +178,50 @@ def build_layer(w, device, torch):
     return layer, x, cent, ln
 
 
+def ref_gpu_baseline(w, torch, sample_experts=8, reps=3):
+    """Times the reference's own kernels + cuBLAS SGEMM in the order MoELayerPlugin::enqueue issues them
+    (oracle/_ref, built from the reference checkout; the TensorRT plugin itself cannot be built here), on a bounded
+    slice of workload `w`: `sample_experts` experts with their share of tokens.  Two figures: the literal behaviour
+    (every used expert copied from pinned host memory on every call) and the same sequence with the copies sourced
+    from device memory."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libinfmoe_ref_kernels.so")
+    if not os.path.exists(path) or w.streamed:
+        return None
+    lib = ctypes.CDLL(path)
+    tpe = max(1, w.tokens // w.expert_count)
+    ws = synth.scaled(w, expert_count=sample_experts, batch=1, seq_len=sample_experts * tpe)
+    T, D, E, F, mc = ws.tokens, ws.embedding_size, ws.expert_count, ws.hidden_size, ws.max_concurrency
+    x, cent, ln = synth.gen_inputs(ws)
+    dev = torch.device("cuda")
+    dx, dc = torch.from_numpy(x).to(dev), torch.from_numpy(cent).to(dev)
+    dl = torch.from_numpy(ln).to(dev) if ln is not None else None
+    on_dev = [synth.gen_expert_torch(ws, e, dev) for e in range(E)]
+    on_host = [[t.cpu().pin_memory() for t in ex] for ex in on_dev]
+    nbytes = mc * (4 * D + 12 * D * F + 4 * T * (D + 2 * F)) + 4 * (T * E + 2 * T + 2 * T * D) + 8 * T + 1024
+    wsp = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(dx)
+    flags = (1 if ws.variant == "cpm_2" else 0) | (2 if ws.variant == "base_layer" else 0) | 4
+    res = {}
+    for label, src, kind in (("streamed_from_pinned_host", on_host, 0), ("weights_on_device", on_dev, 1)):
+        tabs = [(ctypes.c_void_p * E)(*[ex[i].data_ptr() for ex in src]) for i in range(4)]
+        def call():
+            rc = lib.ref_layer_call(T, D, E, F, mc, flags, ctypes.c_void_p(dx.data_ptr()), ctypes.c_void_p(dc.data_ptr()),
+                                    ctypes.c_void_p(dl.data_ptr() if dl is not None else 0), tabs[0], tabs[1], tabs[2],
+                                    tabs[3], kind, ctypes.c_void_p(wsp.data_ptr()), ctypes.c_void_p(out.data_ptr()))
+            assert rc == 0, rc
+        call()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            call()
+        res[label] = {"value": T * reps / (time.perf_counter() - t0), "unit": UNIT}
+    res["sample"] = f"{E} of {w.expert_count} experts x {tpe} tokens of workload {w.name}, max_concurrency {mc}"
+    res["what"] = ("reference kernels (moe.cu, layernorm.cu, gelu.cu) + cublasSgemm_v2 FP32, launch/copy/sync order of "
+                   "MoELayerPlugin::enqueue restated; final gather reads the expert output")
+    return res
+
+
 def run_single(args, w):
     import torch
 
@@ -272,8 +316,10 @@ def run_single(args, w):
         if (stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) > 0 else None,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
     }
-    print(json.dumps(line), flush=True)
     layer.terminate()
+    if not args.no_cpu:
+        line["ref_gpu_baseline"] = ref_gpu_baseline(w, torch)
+    print(json.dumps(line), flush=True)
 
 
 def main():

@@ -161,3 +161,44 @@ def test_reference_gating_against_fused_routing(ref, g, oracle):
     assert diff.size <= 2                                    # FP32 summation order only matters at near-ties
     assert np.all((top1 - top2)[diff] < 1e-5)
     np.testing.assert_allclose(score, wt.cpu().numpy(), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("variant", ["cpm_2", "default", "base_layer"])
+def test_reference_layer_sequence(ref, g, oracle, variant):
+    """The whole launch sequence of MoELayerPlugin::enqueue on the reference's kernels: with the final gather
+    reading the expert output it equals the oracle and this library; literally (gather of the scattered input,
+    plugin/MoELayerPlugin.cc:411) cpm_2/default return their input."""
+    import torch
+    from infmoe_b200 import MoELayer, synth
+    w = synth.scaled(synth.WORKLOADS["tiny_default"], variant=variant, expert_count=6, embedding_size=128,
+                     hidden_size=256, batch=2, seq_len=150)
+    x, c, ln = synth.gen_inputs(w)
+    experts = [synth.gen_expert_numpy(w, e) for e in range(w.expert_count)]
+    T, D, E, F, mc = w.tokens, w.embedding_size, w.expert_count, w.hidden_size, 2
+    dx, dc = g.dev(x), g.dev(c)
+    dl = g.dev(ln) if ln is not None else None
+    dev_w = [[g.dev(a) for a in ex] for ex in experts]
+    tabs = [(ctypes.c_void_p * E)(*[ex[i].data_ptr() for ex in dev_w]) for i in range(4)]
+    nbytes = mc * (4 * D + 12 * D * F + 4 * T * (D + 2 * F)) + 4 * (T * E + 2 * T + 2 * T * D) + 8 * T + 1024
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(dx)
+    base = (1 if variant == "cpm_2" else 0) | (2 if variant == "base_layer" else 0)
+
+    def call(flags):
+        rc = ref.ref_layer_call(T, D, E, F, mc, flags, _p(dx), _p(dc), _p(dl) if dl is not None else None, tabs[0],
+                                tabs[1], tabs[2], tabs[3], 1, _p(ws), _p(out))
+        assert rc == 0
+        return out.cpu().numpy()
+
+    fixed = call(base | 4)
+    r = oracle.layer_forward_f32(x, variant, c, ln, experts)
+    o64 = oracle.layer_forward_f64(x, variant, r["gate"], r["score"], experts)
+    assert oracle.rel_l2(fixed, o64) <= 1e-5
+    layer = MoELayer.create(E, D, F, mc, c, None, "T5_FF", variant, ln)
+    for e, ex in enumerate(experts):
+        layer.set_expert(e, *ex)
+    assert oracle.rel_l2(layer.forward_host(x), fixed) <= 1e-5
+    layer.terminate()
+    if variant != "base_layer":
+        np.testing.assert_array_equal(call(base), x)
+        np.testing.assert_array_equal(oracle.layer_forward_f32(x, variant, c, ln, experts, literal_gather=True)["out"], x)
