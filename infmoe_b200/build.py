@@ -24,7 +24,7 @@ NVCC_FLAGS = ARCH + ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvi
                      "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 CORE_SOURCES = ["route.cu", "dispatch.cu", "rows.cu", "ffn_simt.cu", "ffn_umma.cu", "layer.cu", "npz.cc"]
-PLUGIN_SOURCES = ["plugin/MoELayerPlugin.cc", "plugin/MoELayerPluginCreator.cc"]
+PLUGIN_SOURCES = ["plugin/MoELayerPlugin.cc", "plugin/MoELayerPluginCreator.cc", "plugin/host_driver.cc"]
 
 
 def _nvcc() -> str:
