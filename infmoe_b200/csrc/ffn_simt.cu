@@ -8,9 +8,10 @@
 // its rows [offset[e], offset[e+1]):
 //   g = gelu(h wi_0^T) * (h wi_1^T)        h = h_hi + h_lo (exact recombination)
 //   y = x + g wo^T
-// Operands are stored as TF32 head/tail planes; head + tail is the original
-// FP32 value exactly, so these kernels compute with full FP32 inputs.  wi_0 and
-// wi_1 share one plane pair with interleaved rows (row 2f = wi_0[f], 2f+1 = wi_1[f]).
+// Activations are stored as TF32 head/tail planes; head + tail is the original
+// FP32 value exactly, so these kernels compute with full FP32 inputs.  Weights are
+// raw FP32; wi_0 and wi_1 share one matrix with interleaved rows (row 2f = wi_0[f],
+// row 2f+1 = wi_1[f]).
 #include "common.cuh"
 
 namespace infmoe {
@@ -44,8 +45,7 @@ template <bool DUAL>
 __global__ void __launch_bounds__(256)
 ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, int K,
                 const float* __restrict__ a_hi, const float* __restrict__ a_lo,
-                const float* __restrict__ w_hi, const float* __restrict__ w_lo,
-                const int* __restrict__ slot_of_expert, const float* __restrict__ resid,
+                const float* __restrict__ w, const int* __restrict__ slot_of_expert, const float* __restrict__ resid,
                 float* __restrict__ out_hi, float* __restrict__ out_lo) {
     __shared__ float As[TK][TM + 1];
     __shared__ float B0s[TK][TN + 1];
@@ -88,8 +88,8 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
             float v0 = 0.f, v1 = 0.f;
             if (n0 + n < N && k0 + k < K) {
                 const size_t o = wbase + (size_t)(n0 + n) * K * (DUAL ? 2 : 1) + k0 + k;
-                v0 = w_hi[o] + w_lo[o];
-                if (DUAL) v1 = w_hi[o + K] + w_lo[o + K];
+                v0 = w[o];
+                if (DUAL) v1 = w[o + K];
             }
             B0s[k][n] = v0;
             if (DUAL) B1s[k][n] = v1;
@@ -142,16 +142,15 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
 //   h_hi/h_lo [T][D], g_hi/g_lo [T][F] (scratch), routed [T][D], post [T][D]
 //   slot_of_expert (device, may be NULL = identity) maps expert -> weight slot.
 int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
-                    const float* h_hi, const float* h_lo, const float* w01_hi, const float* w01_lo,
-                    const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi, float* g_lo,
-                    float* post, cudaStream_t stream) {
+                    const float* h_hi, const float* h_lo, const float* w01, const float* wo, const float* routed,
+                    float* g_hi, float* g_lo, float* post, cudaStream_t stream) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     const unsigned row_tiles = (unsigned)((T + TM - 1) / TM + (e_end - e_begin));
     dim3 g1((F + TN - 1) / TN, row_tiles), g2((D + TN - 1) / TN, row_tiles);
-    ffn_simt_kernel<true><<<g1, 256, 0, stream>>>(offset, e_begin, e_end, F, D, h_hi, h_lo, w01_hi, w01_lo,
-                                                  slot_of_expert, nullptr, g_hi, g_lo);
-    ffn_simt_kernel<false><<<g2, 256, 0, stream>>>(offset, e_begin, e_end, D, F, g_hi, g_lo, wo_hi, wo_lo,
-                                                   slot_of_expert, routed, post, nullptr);
+    ffn_simt_kernel<true><<<g1, 256, 0, stream>>>(offset, e_begin, e_end, F, D, h_hi, h_lo, w01, slot_of_expert,
+                                                  nullptr, g_hi, g_lo);
+    ffn_simt_kernel<false><<<g2, 256, 0, stream>>>(offset, e_begin, e_end, D, F, g_hi, g_lo, wo, slot_of_expert,
+                                                   routed, post, nullptr);
     note_launch(2);
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;

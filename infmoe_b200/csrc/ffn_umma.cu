@@ -18,10 +18,17 @@
 // two 128-token tiles, and a decode step with 1..64 tokens runs N=16..64 MMAs.
 // The accumulator is D^T: TMEM lane = weight row, TMEM column = token.
 //
-// 3xTF32.  Every operand is stored as two FP32 planes: hi = x rounded to TF32
-// and lo = x - hi (exact).  Per 8-wide k step three MMAs accumulate
-// lo*hi + hi*lo + hi*hi into the same FP32 accumulator; the dropped lo*lo term
-// is below 2^-22 relative.
+// 3xTF32.  x = hi + lo with hi = x rounded to TF32 and lo = x - hi (exact).
+// Per 8-wide k step three MMAs accumulate lo*hi + hi*lo + hi*hi into the same
+// FP32 accumulator; the dropped lo*lo term is below 2^-22 relative.
+//   * Token operand (N side, read from shared memory by the MMA): the producers of
+//     the activations (scatter + LayerNorm, GEMM-1 epilogue) already write the two
+//     planes, which are small and reused by every weight tile.
+//   * Weight operand (M side): the raw FP32 matrix is streamed from HBM exactly
+//     once.  Four transform warps read each 128 x 32 tile from shared memory, split
+//     it in registers and store head and tail into TMEM (tcgen05.st); the MMA takes
+//     its A operand from TMEM.  Weights therefore cost 4 bytes per element in HBM,
+//     L2 and shared memory, and the MMA reads only the token tile from shared memory.
 //
 // Chunked accumulation.  The tensor core adds into its FP32 accumulator with
 // truncation, not round-to-nearest: measured on B200, one accumulator carried
@@ -32,16 +39,24 @@
 // round-to-nearest adds while the tensor core already works on the next chunk.
 // The same double buffering hides the epilogue behind the next tile's MMAs.
 //
-// Pipeline per CTA (persistent, one CTA per SM, 320 threads):
-//   warp 0      TMA producer: per k block loads the weight tile (box 128 x BK)
-//               and the token tile (boxes 32 x BK) of both planes into a
-//               STAGES-deep shared-memory ring, completion on mbarriers
-//   warp 1      allocates TMEM, issues tcgen05.mma from one lane, commits each
-//               stage back to the producer and each K chunk to the accumulate warps
-//   warps 2..9  accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter
-//               and every other 16-column slice per warp), add into registers; after
-//               the last chunk gelu*dot + TF32 split (lane pairs exchange a and b by
-//               shuffle) or residual add, stores contiguous over the weight-row index
+// Two MMA issuers.  A tf32 MMA of this shape (128 x 144 x 8) runs for only ~72 cycles and the
+// tensor pipe accepts few instructions ahead, so a single issuing thread leaves the pipe idle
+// whenever it waits on a barrier or commits (measured: ~900 of ~1870 cycles per k block).  Two
+// warps therefore issue alternate k blocks.  To make the order of their MMAs irrelevant every MMA
+// accumulates (none overwrites): the accumulate warps clear a TMEM accumulator after draining it.
+//
+// Pipeline per CTA (persistent, one CTA per SM, 16 warps):
+//   warp 0        TMA producer of the weight ring (W_STAGES x 16 KB, raw FP32)
+//   warp 1, 15    MMA issuers for even / odd k blocks (warp 1 also owns the TMEM allocation); a commit
+//                 per k block frees the token stage and the TMEM weight buffer, a commit per K chunk
+//                 hands the accumulator to the accumulate warps
+//   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and
+//                 every other 16-column slice per warp), add into registers, clear the
+//                 columns; after the last chunk gelu*dot + TF32 split (lane pairs exchange a
+//                 and b by shuffle) or residual add, stores contiguous over the weight-row index
+//   warps 10..13  transform: weight tile shared memory -> registers -> hi/lo -> TMEM
+//   warp 14       TMA producer of the token ring (RING stages x two planes)
+// TMEM columns: accumulators at 0 and 160, weight head/tail buffers at 320, 384 and 448.
 // Tiles are (expert, 128-row weight block, token chunk); the list is derived in
 // the kernel from offset[E+1], so no host synchronisation is needed.  Every
 // mbarrier wait is bounded: on expiry the CTA raises STATUS_WAIT_TIMEOUT, lets
@@ -89,7 +104,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the wait was abandoned (limit reached here or in another role).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// The slow path is a real function call (about 200 cycles on B200); the common case, a barrier
+// that is already complete, is a single inlined try_wait (about 17 cycles).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (int i = 0; i < 2048; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
@@ -102,6 +119,13 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile i
             return false;
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
@@ -118,23 +142,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// Brings a weight box into L2 without touching shared memory.
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major, FP32 accumulate.
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T: A is 128 lanes x 8 columns of TF32, B is K-major in shared memory.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Arrives on the mbarrier once all MMAs issued so far by this thread have completed.
@@ -153,23 +171,32 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int BK>
-struct Swz {
-    static_assert(BK == 16 || BK == 32, "BK must give 64- or 128-byte shared-memory rows");
-    static constexpr int ROW_BYTES = BK * 4;
-    static constexpr uint64_t LAYOUT = BK == 32 ? 2 : 4;          // UMMA layout type: SWIZZLE_128B / SWIZZLE_64B
-    static constexpr uint64_t SBO = (8 * ROW_BYTES) >> 4;         // 8-row group pitch, 16-byte units
-};
+// Stores 8 consecutive TMEM columns of this thread's lane.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+// Clears 16 consecutive TMEM columns of this thread's lane.
+__device__ __forceinline__ void tmem_zero16(uint32_t taddr) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major swizzled tile (rows of BK floats, 8-row swizzle groups).
-template <int BK>
+constexpr int BK = 32;                     // k block: 32 floats = one 128-byte swizzled row
+constexpr int ROW_BYTES = BK * 4;
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzled rows (8-row groups of 1024 bytes).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                      // leading byte offset: not used by swizzled K-major layouts
-    d |= Swz<BK>::SBO << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
-    d |= Swz<BK>::LAYOUT << 61;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);    // start address
+    d |= (uint64_t)1 << 16;                       // leading byte offset: not used by swizzled K-major layouts
+    d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
     return d;
 }
 
@@ -180,22 +207,28 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 
 enum { EPI_GELU_PAIR = 0, EPI_RESIDUAL = 1 };
 
-constexpr int EPI_WARPS = 8;                        // two warps per TMEM lane quarter
-constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;  // producer, MMA issuer, accumulate/epilogue warps
-constexpr int ACC_STRIDE = 256;                     // TMEM columns between the two accumulator buffers
+constexpr int EPI_WARPS = 8;                          // two warps per TMEM lane quarter
+constexpr int XF_WARPS = 4;                           // one transform warp per TMEM lane quarter
+constexpr int TOKEN_WARP = 2 + EPI_WARPS + XF_WARPS;  // TMA producer of the token ring
+constexpr int MMA2_WARP = TOKEN_WARP + 1;             // second MMA issuer (odd k blocks)
+constexpr int GEMM_THREADS = (MMA2_WARP + 1) * 32;
+constexpr int ACC_STRIDE = 160;                       // TMEM columns between the two accumulators
+constexpr int WBUF_COL = 2 * ACC_STRIDE;              // first TMEM column of the weight head/tail buffers
+constexpr int WBUF_STRIDE = 2 * BK;                   // head (BK columns) then tail (BK columns)
+constexpr int RING = 3;                               // depth of the token ring and of the TMEM weight buffers
 constexpr int TMEM_COLS = 512;
-constexpr int K_CHUNK = 256;                        // K extent accumulated inside the tensor core at a time
+constexpr int K_CHUNK = 256;                          // K extent accumulated inside the tensor core at a time
+constexpr int KB_PER_CHUNK = K_CHUNK / BK;
+constexpr int W_TILE = UMMA_M * ROW_BYTES;            // 16 KB of raw FP32 weights per k block
 
-template <int BK, int NMAX, int STAGES>
+template <int NMAX, int W_STAGES>
 struct Cfg {
-    static constexpr int W_TILE = UMMA_M * BK * 4;
-    static constexpr int A_TILE = NMAX * BK * 4;
-    static constexpr int STAGE = 2 * W_TILE + 2 * A_TILE;           // hi and lo planes of both operands
-    static constexpr int SMEM = STAGES * STAGE + 1024;              // + slack to align the ring to 1024 bytes
-    static constexpr int KB_PER_CHUNK = K_CHUNK / BK;
+    static constexpr int A_TILE = NMAX * ROW_BYTES;                 // one plane of the token tile
+    static constexpr int A_STAGE = 2 * A_TILE;
+    static constexpr int SMEM = W_STAGES * W_TILE + RING * A_STAGE + 1024;   // + slack for 1024-byte alignment
     static constexpr int SLICES = NMAX / 32;                        // 16-column slices owned by one epilogue thread
     static_assert(NMAX % 32 == 0 && NMAX <= ACC_STRIDE, "token chunk");
-    static_assert(W_TILE % 1024 == 0 && A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
+    static_assert(A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
 };
 
 struct GemmArgs {
@@ -208,7 +241,6 @@ struct GemmArgs {
     float* out_lo;              // GELU_PAIR: g_lo
     const float* resid;         // RESIDUAL: x [T][M_total]
     int* status;
-    int prefetch;               // L2 prefetch distance of the weight stream, in k blocks
 };
 
 struct TileInfo {
@@ -243,17 +275,20 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, c
     return t;
 }
 
-template <int EPI, int BK, int NMAX, int STAGES>
+template <int EPI, int NMAX, int W_STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
-                const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                const GemmArgs args) {
-    using C = Cfg<BK, NMAX, STAGES>;
+ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a_hi,
+                const __grid_constant__ CUtensorMap map_a_lo, const GemmArgs args) {
+    using C = Cfg<NMAX, W_STAGES>;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[STAGES];
-    __shared__ __align__(8) uint64_t s_empty[STAGES];
-    __shared__ __align__(8) uint64_t s_acc_full[2];
-    __shared__ __align__(8) uint64_t s_acc_empty[2];
+    __shared__ __align__(8) uint64_t s_w_full[W_STAGES];    // TMA -> transform
+    __shared__ __align__(8) uint64_t s_w_empty[W_STAGES];   // transform -> TMA
+    __shared__ __align__(8) uint64_t s_a_full[RING];        // TMA -> MMA: token stage filled
+    __shared__ __align__(8) uint64_t s_wb_ready[RING];      // transform -> MMA: TMEM weight buffer filled
+    __shared__ __align__(8) uint64_t s_kb_done[RING];       // MMA -> TMA and transform: the k block's MMAs are done,
+                                                            // its token stage and TMEM weight buffer are free
+    __shared__ __align__(8) uint64_t s_acc_full[2];         // both MMA issuers -> accumulate warps
+    __shared__ __align__(8) uint64_t s_acc_empty[2];        // accumulate warps -> MMA: drained and cleared
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_prefix[MAX_EXPERTS + 1];
@@ -261,6 +296,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t w_ring = ring, a_ring = ring + W_STAGES * W_TILE;
     const int MB = (args.M_total + UMMA_M - 1) / UMMA_M;
     const int KB = (args.K + BK - 1) / BK;
 
@@ -287,12 +323,17 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
         if (lane == 0) s_prefix[args.E] = carry;
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_empty[s]), 1);
+        for (int s = 0; s < W_STAGES; ++s) {
+            mbar_init(smem_u32(&s_w_full[s]), 1);
+            mbar_init(smem_u32(&s_w_empty[s]), XF_WARPS * 32);
+        }
+        for (int s = 0; s < RING; ++s) {
+            mbar_init(smem_u32(&s_a_full[s]), 1);
+            mbar_init(smem_u32(&s_wb_ready[s]), XF_WARPS * 32);
+            mbar_init(smem_u32(&s_kb_done[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&s_acc_full[b]), 1);
+            mbar_init(smem_u32(&s_acc_full[b]), 2);
             mbar_init(smem_u32(&s_acc_empty[b]), EPI_WARPS * 32);
         }
         s_abort = 0;
@@ -312,113 +353,126 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
     volatile int* abort_flag = &s_abort;
 
     if (warp == 0) {
-        // ================= TMA producer =================
-        // Optional L2 prefetch cursor PF k blocks ahead of the loads (INFMOE_GEMM_PREFETCH).  Measured
-        // on B200 it does not help this kernel (the weight stream already runs at ~75% of the copy
-        // bandwidth; distances >= 8 k blocks thrash L2), so it is off by default.
+        // ================= TMA producer, weights =================
+        // Runs up to W_STAGES k blocks ahead of the transform warps, independently of the token ring.
         if (lane == 0) {
-            const int PF = args.prefetch;    // look-ahead in k blocks
             uint32_t it = 0;
-            int la_tile = blockIdx.x, la_kb = 0, la_m0 = 0, la_slot = 0;
-            bool la_valid = la_tile < total_tiles;
-            if (la_valid) {
-                const TileInfo t = decode_tile<NMAX>(la_tile, s_prefix, args);
-                la_m0 = t.mb * UMMA_M;
-                la_slot = t.slot;
-            }
-            auto prefetch_next = [&]() {
-                if (!la_valid) return;
-                tma_prefetch_3d(&map_w_hi, la_kb * BK, la_m0, la_slot);
-                tma_prefetch_3d(&map_w_lo, la_kb * BK, la_m0, la_slot);
-                if (++la_kb == KB) {
-                    la_kb = 0;
-                    la_tile += gridDim.x;
-                    la_valid = la_tile < total_tiles;
-                    if (la_valid) {
-                        const TileInfo t = decode_tile<NMAX>(la_tile, s_prefix, args);
-                        la_m0 = t.mb * UMMA_M;
-                        la_slot = t.slot;
-                    }
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+                bool ok = true;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % W_STAGES;
+                    if (!mbar_wait(smem_u32(&s_w_empty[s]), ((it / W_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&s_w_full[s]);
+                    mbar_expect_tx(bar, W_TILE);
+                    tma_load_3d(w_ring + s * W_TILE, &map_w, bar, kb * BK, t.mb * UMMA_M, t.slot);
                 }
-            };
-            for (int i = 0; i < PF; ++i) prefetch_next();
+                if (!ok) break;
+            }
+        }
+    } else if (warp == TOKEN_WARP) {
+        // ================= TMA producer, tokens (head and tail planes) =================
+        if (lane == 0) {
+            uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
                 const int nbox = (t.n_pad + 31) >> 5;
-                const uint32_t bytes = 2 * C::W_TILE + 2 * nbox * 32 * BK * 4;
+                const uint32_t a_bytes = 2 * nbox * 32 * ROW_BYTES;
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    prefetch_next();
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
-                    const uint32_t bar = smem_u32(&s_full[s]);
-                    mbar_expect_tx(bar, bytes);
-                    const uint32_t base = ring + s * C::STAGE;
-                    const int k0 = kb * BK, m0 = t.mb * UMMA_M;
-                    tma_load_3d(base, &map_w_hi, bar, k0, m0, t.slot);
-                    tma_load_3d(base + C::W_TILE, &map_w_lo, bar, k0, m0, t.slot);
-                    const uint32_t a_hi = base + 2 * C::W_TILE, a_lo = a_hi + C::A_TILE;
+                    const int s = it % RING;
+                    if (!mbar_wait(smem_u32(&s_kb_done[s]), ((it / RING) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&s_a_full[s]);
+                    mbar_expect_tx(bar, a_bytes);
+                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
                     for (int b = 0; b < nbox; ++b) {
-                        tma_load_2d(a_hi + b * 32 * BK * 4, &map_a_hi, bar, k0, t.row0 + b * 32);
-                        tma_load_2d(a_lo + b * 32 * BK * 4, &map_a_lo, bar, k0, t.row0 + b * 32);
+                        tma_load_2d(a_hi + b * 32 * ROW_BYTES, &map_a_hi, bar, kb * BK, t.row0 + b * 32);
+                        tma_load_2d(a_lo + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * BK, t.row0 + b * 32);
                     }
                 }
                 if (!ok) break;
             }
         }
-    } else if (warp == 1) {
-        // ================= MMA issuer =================
-        if (lane == 0) {
-            uint32_t it = 0, chunk = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
-                const uint32_t idesc = make_idesc(t.n_pad);
-                bool ok = true;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int kc = kb % C::KB_PER_CHUNK;
-                    const uint32_t buf = chunk & 1;
-                    if (kc == 0) {  // a new K chunk starts in accumulator `buf`: it must have been drained
-                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), ((chunk >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                        tc_fence_after();
+    } else if (warp == 1 || warp == MMA2_WARP) {
+        // ================= MMA issuers =================
+        // Both warps walk every k block; warp 1 issues the even ones, the other warp the odd ones
+        // (by the CTA-wide k block counter).  The whole warp runs the loop so that addresses and
+        // descriptors stay warp-uniform; one lane issues the tcgen05 instructions.  All MMAs
+        // accumulate into an accumulator the accumulate warps have cleared, so the interleaving
+        // of the two issuers does not matter.
+        const uint32_t mine = warp == 1 ? 0u : 1u;
+        const bool leader = lane == 0;
+        uint32_t it = 0, chunk = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+            const uint32_t idesc = make_idesc(t.n_pad);
+            bool ok = true, entered = false;   // entered: this warp has already waited for the chunk's accumulator
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int kc = kb % KB_PER_CHUNK;
+                const uint32_t buf = chunk & 1;
+                if (kc == 0) entered = false;
+                if ((it & 1u) == mine) {
+                    if (!entered) {  // the accumulator of this chunk must have been drained and cleared
+                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
+                        entered = true;
                     }
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&s_full[s]), ph, abort_flag)) { ok = false; break; }
+                    const int s = it % RING;
+                    const uint32_t ph = (it / RING) & 1;
+                    if (!mbar_wait(smem_u32(&s_a_full[s]), ph, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&s_wb_ready[s]), ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t base = ring + s * C::STAGE;
-                    const uint32_t a_hi = base + 2 * C::W_TILE, a_lo = a_hi + C::A_TILE;
+                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
                     const uint32_t d = tmem_base + buf * ACC_STRIDE;
+                    const uint32_t w_hi = tmem_base + WBUF_COL + s * WBUF_STRIDE, w_lo = w_hi + BK;
+                    const uint64_t d_a_hi = make_smem_desc(a_hi), d_a_lo = make_smem_desc(a_lo);
+                    if (leader) {
 #pragma unroll
-                    for (int ks = 0; ks < BK / 8; ++ks) {
-                        const uint32_t koff = ks * 32;  // 8 TF32 = 32 bytes along K inside the swizzled row
-                        const uint64_t d_a_hi = make_smem_desc<BK>(a_hi + koff);
-                        const uint64_t d_a_lo = make_smem_desc<BK>(a_lo + koff);
-                        const uint64_t d_w_hi = make_smem_desc<BK>(base + koff);
-                        const uint64_t d_w_lo = make_smem_desc<BK>(base + C::W_TILE + koff);
-                        umma_tf32(d, d_w_lo, d_a_hi, idesc, (kc | ks) ? 1u : 0u);   // small terms first
-                        umma_tf32(d, d_w_hi, d_a_lo, idesc, 1u);
-                        umma_tf32(d, d_w_hi, d_a_hi, idesc, 1u);
-                    }
-                    umma_commit(smem_u32(&s_empty[s]));  // stage reusable once these MMAs have read it
-                    if (kc == C::KB_PER_CHUNK - 1 || kb == KB - 1) {
-                        umma_commit(smem_u32(&s_acc_full[buf]));  // chunk complete: hand it to the accumulate warps
-                        ++chunk;
+                        for (int ks = 0; ks < BK / 8; ++ks) {
+                            // 8 TF32 = 32 bytes along K inside the swizzled row = 2 units of the descriptor address
+                            const uint64_t b_hi = d_a_hi + 2 * ks, b_lo = d_a_lo + 2 * ks;
+                            umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, 1u);   // small terms first
+                            umma_tf32_ts(d, w_hi + ks * 8, b_lo, idesc, 1u);
+                            umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
+                        }
+                        // token stage and TMEM weight buffer are free once these MMAs have completed
+                        umma_commit(smem_u32(&s_kb_done[s]));
                     }
                 }
-                if (!ok) break;
+                if (kc == KB_PER_CHUNK - 1 || kb == KB - 1) {
+                    // chunk complete for this issuer: its MMAs of the chunk (if any) gate the hand-over
+                    if (!entered) {
+                        // nothing of this chunk was issued here (a one-block tail chunk); still wait for the
+                        // accumulator's previous round to be over so that this arrival counts for the right phase
+                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
+                        if (leader) mbar_arrive(smem_u32(&s_acc_full[buf]));
+                    } else if (leader) {
+                        umma_commit(smem_u32(&s_acc_full[buf]));
+                    }
+                    ++chunk;
+                }
             }
+            if (!ok) break;
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ================= accumulate + epilogue (warps 2..9) =================
-        // The tensor core adds into its FP32 accumulator with truncation, so a long K loop inside
-        // TMEM drifts.  Each K chunk is therefore accumulated from zero in TMEM and added to a
-        // running sum in registers with round-to-nearest adds.
-        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        // Each K chunk is accumulated in TMEM from a cleared accumulator and added here, with
+        // round-to-nearest adds, to a running sum in registers; the columns are cleared again
+        // before the accumulator goes back to the MMA issuers.
+        const int q = warp & 3;                 // TMEM lane quarter this warp may access
         const int half = (warp - 2) >> 2;       // even or odd 16-column slices
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
+        // first hand-over: both accumulators cleared
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int i = 0; i < C::SLICES; ++i) tmem_zero16(tlane + b * ACC_STRIDE + (2 * i + half) * 16);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&s_acc_empty[0]));
+        mbar_arrive(smem_u32(&s_acc_empty[1]));
         uint32_t chunk = 0;
-        const int NC = (KB + C::KB_PER_CHUNK - 1) / C::KB_PER_CHUNK;
+        const int NC = (KB + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
             const int nsl = t.n_pad >> 4;
@@ -439,10 +493,12 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
                         uint32_t r[16];
                         tmem_ld16(tlane + buf * ACC_STRIDE + sl * 16, r);
                         tmem_ld_wait();
+                        tmem_zero16(tlane + buf * ACC_STRIDE + sl * 16);
 #pragma unroll
                         for (int c = 0; c < 16; ++c) sum[i][c] = __fadd_rn(sum[i][c], __uint_as_float(r[c]));
                     }
                 }
+                tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(smem_u32(&s_acc_empty[buf]));
             }
@@ -475,6 +531,51 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __grid_const
                     }
                 }
             }
+        }
+    } else {
+        // ================= transform (warps 10..13) =================
+        // Thread = one weight row of the tile.  The row's 128 bytes are read from the swizzled
+        // shared-memory tile (16-byte chunk c of row r sits at chunk c ^ (r & 7)), split into
+        // TF32 head and tail, and stored into this thread's TMEM lane.
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + WBUF_COL;
+        const uint8_t* w_ring_ptr = smem_raw + (w_ring - smem_u32(smem_raw));
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+            bool ok = true;
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int s = it % W_STAGES;
+                const uint32_t wb = it % RING;
+                if (!mbar_wait(smem_u32(&s_w_full[s]), (it / W_STAGES) & 1, abort_flag)) { ok = false; break; }
+                const uint8_t* row = w_ring_ptr + s * W_TILE + r * ROW_BYTES;
+                float4 v[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
+                mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
+                // the MMAs that read this TMEM buffer RING k blocks ago must be done
+                if (!mbar_wait(smem_u32(&s_kb_done[wb]), ((it / RING) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t dst = tlane + wb * WBUF_STRIDE;
+#pragma unroll
+                for (int c = 0; c < 8; c += 2) {
+                    uint32_t hi[8], lo[8];
+                    const float x[8] = {v[c].x, v[c].y, v[c].z, v[c].w, v[c + 1].x, v[c + 1].y, v[c + 1].z, v[c + 1].w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float h, l;
+                        split_tf32(x[j], h, l);
+                        hi[j] = __float_as_uint(h);
+                        lo[j] = __float_as_uint(l);
+                    }
+                    tmem_st8(dst + c * 4, hi);
+                    tmem_st8(dst + BK + c * 4, lo);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(smem_u32(&s_wb_ready[wb]));
+            }
+            if (!ok) break;
         }
     }
 
@@ -514,9 +615,8 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// rank-3 map over a plane [slots][rows][K] (K contiguous); box = BK x box_rows x 1
-int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uint64_t slots, int bk, int box_rows,
-             int rank) {
+// map over a plane [slots][rows][K] (K contiguous); box = BK x box_rows (x 1), 128-byte swizzle
+int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uint64_t slots, int box_rows, int rank) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -524,33 +624,31 @@ int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uin
     }
     cuuint64_t dims[3] = {K, rows, slots};
     cuuint64_t strides[2] = {K * 4, K * rows * 4};
-    cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 1};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapSwizzle swz = bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, (void*)base, dims, strides, box,
-                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with %d (K=%llu rows=%llu slots=%llu box=%dx%d)", (int)r,
-                  (unsigned long long)K, (unsigned long long)rows, (unsigned long long)slots, bk, box_rows);
+                  (unsigned long long)K, (unsigned long long)rows, (unsigned long long)slots, BK, box_rows);
         return INFMOE_ERR_CUDA;
     }
     return INFMOE_OK;
 }
 
-template <int EPI, int BK, int NMAX, int STAGES>
-int launch_one(const GemmArgs& args, long long T, int slots, const float* w_hi, const float* w_lo, const float* a_hi,
-               const float* a_lo, int num_ctas, cudaStream_t stream) {
-    using C = Cfg<BK, NMAX, STAGES>;
-    static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory ring too large");
-    CUtensorMap m[4];
-    INFMOE_TRY(make_map(&m[0], w_hi, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[1], w_lo, args.K, args.M_total, slots, BK, UMMA_M, 3));
-    INFMOE_TRY(make_map(&m[2], a_hi, args.K, (uint64_t)T, 1, BK, 32, 2));
-    INFMOE_TRY(make_map(&m[3], a_lo, args.K, (uint64_t)T, 1, BK, 32, 2));
-    auto kern = ffn_umma_kernel<EPI, BK, NMAX, STAGES>;
+template <int EPI, int NMAX, int W_STAGES>
+int launch_one(const GemmArgs& args, long long T, int slots, const float* w, const float* a_hi, const float* a_lo,
+               int num_ctas, cudaStream_t stream) {
+    using C = Cfg<NMAX, W_STAGES>;
+    static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory rings too large");
+    CUtensorMap m[3];
+    INFMOE_TRY(make_map(&m[0], w, args.K, args.M_total, slots, UMMA_M, 3));
+    INFMOE_TRY(make_map(&m[1], a_hi, args.K, (uint64_t)T, 1, 32, 2));
+    INFMOE_TRY(make_map(&m[2], a_lo, args.K, (uint64_t)T, 1, 32, 2));
+    auto kern = ffn_umma_kernel<EPI, NMAX, W_STAGES>;
     INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], args);
+    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], args);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -564,11 +662,11 @@ bool ffn_umma_supported(int D, int F, int E) {
 
 // Grouped FFN over experts [e_begin, e_end); T rows in expert-contiguous order.
 //   h_hi/h_lo [T][D], g_hi/g_lo [T][F] (scratch), routed [T][D], post [T][D]
-//   w01 planes [slots][2F][D]: row 2f = wi_0[f], row 2f+1 = wi_1[f];  wo planes [slots][D][F]
+//   w01 [slots][2F][D] raw FP32: row 2f = wi_0[f], row 2f+1 = wi_1[f];  wo [slots][D][F] raw FP32
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
-                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01_hi,
-                    const float* w01_lo, const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi,
-                    float* g_lo, float* post, int* status, int num_sms, cudaStream_t stream, cudaEvent_t mid_event) {
+                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
+                    const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
+                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     if (!ffn_umma_supported(D, F, E)) {
         set_error("ffn_umma: unsupported shape D=%d F=%d E=%d", D, F, E);
@@ -586,36 +684,28 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a1.out_lo = g_lo;
     a1.resid = nullptr;
     a1.status = status;
-    static const int prefetch = [] {
-        const char* v = getenv("INFMOE_GEMM_PREFETCH");
-        return v ? atoi(v) : 0;
-    }();
-    a1.prefetch = prefetch;
     GemmArgs a2 = a1;
     a2.M_total = D;
     a2.K = F;
     a2.out_hi = post;
     a2.out_lo = nullptr;
     a2.resid = routed;
-    // Tile shape: k block (floats), token chunk, pipeline depth.  INFMOE_GEMM_TILE selects another
-    // instantiation for tuning runs.
+    // Shapes: token chunk, weight stages (16 KB each).  INFMOE_GEMM_TILE selects another instantiation
+    // for tuning runs.
     static const int variant = [] {
         const char* v = getenv("INFMOE_GEMM_TILE");
         return v ? atoi(v) : 0;
     }();
-#define INFMOE_LAUNCH_PAIR(BK, NMAX, STAGES)                                                                        \
-    do {                                                                                                             \
-        INFMOE_TRY((launch_one<EPI_GELU_PAIR, BK, NMAX, STAGES>(a1, T, slots, w01_hi, w01_lo, h_hi, h_lo, num_sms,    \
-                                                                stream)));                                           \
-        if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));                                          \
-        INFMOE_TRY((launch_one<EPI_RESIDUAL, BK, NMAX, STAGES>(a2, T, slots, wo_hi, wo_lo, g_hi, g_lo, num_sms,       \
-                                                               stream)));                                            \
+#define INFMOE_LAUNCH_PAIR(NMAX, WS)                                                                         \
+    do {                                                                                                      \
+        INFMOE_TRY((launch_one<EPI_GELU_PAIR, NMAX, WS>(a1, T, slots, w01, h_hi, h_lo, num_sms, stream)));    \
+        if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));                                   \
+        INFMOE_TRY((launch_one<EPI_RESIDUAL, NMAX, WS>(a2, T, slots, wo, g_hi, g_lo, num_sms, stream)));      \
     } while (0)
     switch (variant) {
-        case 1: INFMOE_LAUNCH_PAIR(32, 192, 2); break;
-        case 2: INFMOE_LAUNCH_PAIR(16, 192, 5); break;
-        case 3: INFMOE_LAUNCH_PAIR(16, 256, 4); break;
-        default: INFMOE_LAUNCH_PAIR(32, 160, 3); break;   // 128-byte rows: fewest TMA requests per byte
+        case 1: INFMOE_LAUNCH_PAIR(160, 3); break;
+        case 2: INFMOE_LAUNCH_PAIR(128, 6); break;
+        default: INFMOE_LAUNCH_PAIR(160, 5); break;
     }
 #undef INFMOE_LAUNCH_PAIR
     return INFMOE_OK;

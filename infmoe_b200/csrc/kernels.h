@@ -27,18 +27,16 @@ int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_
 int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
                     cudaStream_t stream);
 
-// Expert weights live in four planes: w01_hi/w01_lo [slots][2F][D] (row 2f = wi_0[f], row 2f+1 = wi_1[f])
-// and wo_hi/wo_lo [slots][D][F]; hi = value rounded to TF32, lo = value - hi.
+// Expert weights live in two raw FP32 planes: w01 [slots][2F][D] (row 2f = wi_0[f], row 2f+1 = wi_1[f]) and
+// wo [slots][D][F].  Activations travel as TF32 head/tail planes (hi = value rounded to TF32, lo = value - hi).
 int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
-                    const float* h_hi, const float* h_lo, const float* w01_hi, const float* w01_lo,
-                    const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi, float* g_lo,
-                    float* post, cudaStream_t stream);
+                    const float* h_hi, const float* h_lo, const float* w01, const float* wo, const float* routed,
+                    float* g_hi, float* g_lo, float* post, cudaStream_t stream);
 
 bool ffn_umma_supported(int D, int F, int E);
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
-                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01_hi,
-                    const float* w01_lo, const float* wo_hi, const float* wo_lo, const float* routed, float* g_hi,
-                    float* g_lo, float* post, int* status, int num_sms, cudaStream_t stream,
-                    cudaEvent_t mid_event = nullptr);
+                    const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
+                    const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
+                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event = nullptr);
 
 }  // namespace infmoe

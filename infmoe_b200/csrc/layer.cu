@@ -63,16 +63,16 @@ struct ExpertStore {
     // device: LayerNorm weights of all experts [E][D] (always resident, 4*E*D bytes)
     float* d_ln = nullptr;
     std::vector<char> ln_on_device;
-    // device-resident TF32 head/tail planes:
-    //   [0],[1] w01_hi, w01_lo [E][2F][D]  (row 2f = wi_0[f], row 2f+1 = wi_1[f])
-    //   [2],[3] wo_hi,  wo_lo  [E][D][F]
-    float* d_plane[4] = {nullptr, nullptr, nullptr, nullptr};
+    // device-resident raw FP32 weights:
+    //   [0] w01 [E][2F][D]  (row 2f = wi_0[f], row 2f+1 = wi_1[f])
+    //   [1] wo  [E][D][F]
+    float* d_plane[2] = {nullptr, nullptr};
     std::vector<char> on_device;
     bool fortran_warning = false;
 
     size_t matrix_elems() const { return (size_t)D * (size_t)F; }
-    size_t plane_elems(int p) const { return (p < 2 ? 2 : 1) * matrix_elems(); }   // per expert
-    size_t resident_bytes() const { return 6 * matrix_elems() * (size_t)E * sizeof(float); }
+    size_t plane_elems(int p) const { return (p == 0 ? 2 : 1) * matrix_elems(); }   // per expert
+    size_t resident_bytes() const { return 3 * matrix_elems() * (size_t)E * sizeof(float); }
 
     ~ExpertStore() {
         for (auto& v : {&h_ln, &h_wi0, &h_wi1, &h_wo})
@@ -182,7 +182,7 @@ WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     w.h_lo = take(4 * t * D);
     w.g_hi = take(4 * t * F);
     w.g_lo = take(4 * t * F);
-    w.slots = take(streamed && !L->identity ? 6 * (size_t)L->mc * D * F * 4 : 0);
+    w.slots = take(streamed && !L->identity ? 3 * (size_t)L->mc * D * F * 4 : 0);
     w.total = o;
     return w;
 }
@@ -205,21 +205,19 @@ int ensure_store_device_ln(ExpertStore* s) {
 }
 
 int ensure_resident_planes(ExpertStore* s) {
-    for (int p = 0; p < 4; ++p)
+    for (int p = 0; p < 2; ++p)
         if (!s->d_plane[p]) INFMOE_CUDA_TRY(cudaMalloc(&s->d_plane[p], sizeof(float) * s->plane_elems(p) * s->E));
     return INFMOE_OK;
 }
 
-// Puts one expert's raw matrices into its four planes: wi_0 / wi_1 rows interleaved into the
-// w01 head plane by two strided copies, wo into its head plane, then an in-place head/tail split.
-int load_expert_planes(int D, int F, const float* wi0, const float* wi1, const float* wo, float* w01_hi,
-                       float* w01_lo, float* wo_hi, float* wo_lo, cudaMemcpyKind kind, cudaStream_t stream) {
+// Puts one expert's matrices into its two planes: wi_0 / wi_1 rows interleaved into w01 by two strided
+// copies, wo as it is.  The weights stay raw FP32 (the GEMM kernel splits them on the fly).
+int load_expert_planes(int D, int F, const float* wi0, const float* wi1, const float* wo, float* w01, float* wo_dst,
+                       cudaMemcpyKind kind, cudaStream_t stream) {
     const size_t row = sizeof(float) * (size_t)D;
-    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01_hi, 2 * row, wi0, row, row, (size_t)F, kind, stream));
-    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01_hi + D, 2 * row, wi1, row, row, (size_t)F, kind, stream));
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(wo_hi, wo, sizeof(float) * (size_t)D * F, kind, stream));
-    INFMOE_TRY(launch_split(w01_hi, w01_hi, w01_lo, 2 * (size_t)D * F, stream));
-    INFMOE_TRY(launch_split(wo_hi, wo_hi, wo_lo, (size_t)D * F, stream));
+    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01, 2 * row, wi0, row, row, (size_t)F, kind, stream));
+    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01 + D, 2 * row, wi1, row, row, (size_t)F, kind, stream));
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(wo_dst, wo, sizeof(float) * (size_t)D * F, kind, stream));
     return INFMOE_OK;
 }
 
@@ -230,8 +228,7 @@ int upload_resident(ExpertStore* s, cudaStream_t stream) {
     for (int e = 0; e < s->E; ++e) {
         if (s->on_device[e] || !s->on_host[e]) continue;
         INFMOE_TRY(load_expert_planes(s->D, s->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e], s->d_plane[0] + 2 * n * e,
-                                      s->d_plane[1] + 2 * n * e, s->d_plane[2] + n * e, s->d_plane[3] + n * e,
-                                      cudaMemcpyHostToDevice, stream));
+                                      s->d_plane[1] + n * e, cudaMemcpyHostToDevice, stream));
         s->on_device[e] = 1;
     }
     return INFMOE_OK;
@@ -322,15 +319,14 @@ int status_to_rc(int status) {
 }
 
 int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_offset, const int* d_slot_map,
-            int slots, float* const planes[4], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
+            int slots, float* const planes[2], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
             float* g_lo, float* post, cudaStream_t stream, cudaEvent_t mid = nullptr) {
     const bool umma = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);
     if (umma)
         return launch_ffn_umma(T, L->D, L->F, L->E, e_begin, e_end, d_offset, d_slot_map, slots, h_hi, h_lo, planes[0],
-                               planes[1], planes[2], planes[3], routed, g_hi, g_lo, post, L->d_status, L->num_sms,
-                               stream, mid);
+                               planes[1], routed, g_hi, g_lo, post, L->d_status, L->num_sms, stream, mid);
     return launch_ffn_simt(T, L->D, L->F, e_begin, e_end, d_offset, d_slot_map, h_hi, h_lo, planes[0], planes[1],
-                           planes[2], planes[3], routed, g_hi, g_lo, post, stream);
+                           routed, g_hi, g_lo, post, stream);
 }
 
 void free_device_state(infmoe_layer* L) {
@@ -553,8 +549,8 @@ int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const
         INFMOE_TRY(ensure_resident_planes(s));
         INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln + (size_t)e * s->D, ln_w, sizeof(float) * s->D, cudaMemcpyDeviceToDevice));
         s->ln_on_device[e] = 1;
-        INFMOE_TRY(load_expert_planes(s->D, s->F, wi0, wi1, wo, s->d_plane[0] + 2 * n * e, s->d_plane[1] + 2 * n * e,
-                                      s->d_plane[2] + n * e, s->d_plane[3] + n * e, cudaMemcpyDeviceToDevice, 0));
+        INFMOE_TRY(load_expert_planes(s->D, s->F, wi0, wi1, wo, s->d_plane[0] + 2 * n * e, s->d_plane[1] + n * e,
+                                      cudaMemcpyDeviceToDevice, 0));
         INFMOE_CUDA_TRY(cudaStreamSynchronize(0));
         s->on_device[e] = 1;
     } else {
@@ -684,12 +680,10 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                                stream, mid));
         } else {
             const size_t n = s->matrix_elems();
-            // slot planes: w01_hi, w01_lo [mc][2F][D], then wo_hi, wo_lo [mc][D][F]
-            float* planes[4];
+            // slot planes: w01 [mc][2F][D], then wo [mc][D][F]
+            float* planes[2];
             planes[0] = (float*)(base + w.slots);
             planes[1] = planes[0] + 2 * n * L->mc;
-            planes[2] = planes[1] + 2 * n * L->mc;
-            planes[3] = planes[2] + n * L->mc;
             // the one host synchronisation of the streamed path: which experts have rows?
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_count, count, sizeof(int) * L->E, cudaMemcpyDeviceToHost, stream));
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
@@ -719,8 +713,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                 // the slot is free once the expert that used it (j - mc) has run
                 if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
                 INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e],
-                                              planes[0] + 2 * n * slot, planes[1] + 2 * n * slot, planes[2] + n * slot,
-                                              planes[3] + n * slot, cudaMemcpyHostToDevice, cs));
+                                              planes[0] + 2 * n * slot, planes[1] + n * slot, cudaMemcpyHostToDevice,
+                                              cs));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
                 INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
                 INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, L->mc, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
@@ -1087,7 +1081,7 @@ int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* byte
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + 2 * align_up(8 * d * f) + 2 * align_up(4 * d * f) +
+    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + align_up(8 * d * f) + align_up(4 * d * f) +
              2 * ALIGN + ALIGN;
     return INFMOE_OK;
 }
@@ -1117,30 +1111,27 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
     float* h_lo = (float*)take(4 * r * d);
     float* g_hi = (float*)take(4 * r * f);
     float* g_lo = (float*)take(4 * r * f);
-    float* planes[4];
+    float* planes[2];
     planes[0] = (float*)take(8 * d * f);
-    planes[1] = (float*)take(8 * d * f);
-    planes[2] = (float*)take(4 * d * f);
-    planes[3] = (float*)take(4 * d * f);
+    planes[1] = (float*)take(4 * d * f);
     int* offset = (int*)take(8);
     int* status = (int*)take(4);
     const int h_offset[2] = {0, (int)rows};
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], planes[2], planes[3],
-                                  cudaMemcpyDeviceToDevice, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], cudaMemcpyDeviceToDevice, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const char* path = getenv("INFMOE_FFN");
     const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
     if (simt)
-        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], x, g_hi, g_lo, y, stream));
+        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
+                                   y, stream));
     else
-        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], x, g_hi, g_lo, y, status, sms, stream));
+        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], x, g_hi,
+                                   g_lo, y, status, sms, stream));
     int h_status = 0;
     INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
@@ -1157,7 +1148,7 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
 // device, is refused during capture, and would break an engine whose memory plan was fixed when
 // it was built.  infmoe_t5ff_run needs a caller-provided workspace, which such a caller has to
 // have planned for in advance.  infmoe_t5ff_run_static needs none: its scratch (LayerNorm output,
-// gate activations, the TF32 head/tail copies of the three weight matrices) lives in the array
+// gate activations, the row-interleaved copy of the weight matrices) lives in the array
 // below, which is part of the library image.  Every GPU that loads the library keeps these
 // INFMOE_STATIC_SCRATCH_BYTES resident until the process exits, so the size is deliberately modest;
 // larger problems are rejected and belong to infmoe_t5ff_run.
@@ -1234,11 +1225,9 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     float* h_lo = (float*)take(4 * r * d);
     float* g_hi = (float*)take(4 * r * f);
     float* g_lo = (float*)take(4 * r * f);
-    float* planes[4];
+    float* planes[2];
     planes[0] = (float*)take(8 * d * f);
-    planes[1] = (float*)take(8 * d * f);
-    planes[2] = (float*)take(4 * d * f);
-    planes[3] = (float*)take(4 * d * f);
+    planes[1] = (float*)take(4 * d * f);
     int* offset = (int*)take(8);
     int* status = (int*)take(4);
     // The array keeps whatever the previous call left: everything read below is rewritten first
@@ -1247,19 +1236,18 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], planes[2], planes[3],
-                                  cudaMemcpyDeviceToDevice, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], cudaMemcpyDeviceToDevice, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const char* path = getenv("INFMOE_FFN");
     const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
     if (simt)
-        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], x, g_hi, g_lo, y, stream));
+        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
+                                   y, stream));
     else
-        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], planes[2],
-                                   planes[3], x, g_hi, g_lo, y, status, sms, stream));
+        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], x, g_hi,
+                                   g_lo, y, status, sms, stream));
     int h_status = 0;
     INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));

@@ -77,8 +77,8 @@ def test_workspace_size_formula():
     layer = _layer()
     small, big = layer.get_workspace_size(1), layer.get_workspace_size(100)
     assert 0 < small < big
-    # activations: routed, post, h_hi, h_lo [T][D] and g_hi, g_lo [T][F]; slots: 6 planes x mc x D x F
-    assert big >= 4 * 100 * (4 * 8 + 2 * 16) + 6 * 2 * 8 * 16 * 4
+    # activations: routed, post, h_hi, h_lo [T][D] and g_hi, g_lo [T][F]; slots: mc x 3 matrices of D x F
+    assert big >= 4 * 100 * (4 * 8 + 2 * 16) + 3 * 2 * 8 * 16 * 4
 
 
 def test_python_binding_surface(tmp_path):
