@@ -330,9 +330,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--seq-len", type=int, default=None, help="override the workload's sequence length (tuning)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w, scaling = resolve_workload(args)
+    if args.seq_len:
+        w = synth.scaled(w, seq_len=args.seq_len)
     if args.impl == "reference":
         run_reference_arm(args, w, scaling)
         return

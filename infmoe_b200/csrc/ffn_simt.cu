@@ -10,8 +10,8 @@
 //   y = x + g wo^T
 // Activations are stored as TF32 head/tail planes; head + tail is the original
 // FP32 value exactly, so these kernels compute with full FP32 inputs.  Weights are
-// raw FP32; wi_0 and wi_1 share one matrix with interleaved rows (row 2f = wi_0[f],
-// row 2f+1 = wi_1[f]).
+// raw FP32 in the tile-contiguous layout of the tensor-core path; wi_0 and wi_1 share
+// one matrix with interleaved rows (row 2f = wi_0[f], row 2f+1 = wi_1[f]).
 #include "common.cuh"
 
 namespace infmoe {
@@ -64,7 +64,12 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
     const int expert = s_info[1], row0 = s_info[2], rows = s_info[3];
     const int slot = slot_of_expert ? slot_of_expert[expert] : expert;
     const int n0 = blockIdx.x * TN;
-    const size_t wbase = (size_t)slot * (size_t)N * (size_t)K * (DUAL ? 2 : 1);
+    // tile-contiguous weight plane: 128 x 32 tiles, tile (mb, kb) at (mb * KB + kb) * 4096 floats
+    const int Mw = DUAL ? 2 * N : N, MBw = (Mw + 127) / 128, KBw = (K + 31) / 32;
+    const size_t wbase = (size_t)slot * (size_t)MBw * (size_t)KBw * 4096;
+    auto w_at = [&](int m, int k) -> float {
+        return w[wbase + ((size_t)(m >> 7) * KBw + (k >> 5)) * 4096 + (size_t)(m & 127) * 32 + (k & 31)];
+    };
 
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     float acc0[4][4], acc1[4][4];
@@ -87,9 +92,12 @@ ffn_simt_kernel(const int* __restrict__ offset, int e_begin, int e_end, int N, i
             const int n = i / TK, k = i % TK;
             float v0 = 0.f, v1 = 0.f;
             if (n0 + n < N && k0 + k < K) {
-                const size_t o = wbase + (size_t)(n0 + n) * K * (DUAL ? 2 : 1) + k0 + k;
-                v0 = w[o];
-                if (DUAL) v1 = w[o + K];
+                if (DUAL) {
+                    v0 = w_at(2 * (n0 + n), k0 + k);
+                    v1 = w_at(2 * (n0 + n) + 1, k0 + k);
+                } else {
+                    v0 = w_at(n0 + n, k0 + k);
+                }
             }
             B0s[k][n] = v0;
             if (DUAL) B1s[k][n] = v1;

@@ -25,37 +25,42 @@
 //     the activations (scatter + LayerNorm, GEMM-1 epilogue) already write the two
 //     planes, which are small and reused by every weight tile.
 //   * Weight operand (M side): the raw FP32 matrix is streamed from HBM exactly
-//     once.  Four transform warps read each 128 x 32 tile from shared memory, split
-//     it in registers and store head and tail into TMEM (tcgen05.st); the MMA takes
+//     once, from a tile-contiguous copy made at load time (each 128 x 32 tile is 16 KB
+//     of consecutive addresses, and a CTA's tiles follow one another).  Four transform warps read each
+//     tile from shared memory, split it in registers and store head and tail into TMEM (tcgen05.st); the MMA takes
 //     its A operand from TMEM.  Weights therefore cost 4 bytes per element in HBM,
 //     L2 and shared memory, and the MMA reads only the token tile from shared memory.
 //
 // Chunked accumulation.  The tensor core adds into its FP32 accumulator with
 // truncation, not round-to-nearest: measured on B200, one accumulator carried
 // over K = 1024..2048 drifts by about 1.5e-5 relative, and the drift grows
-// linearly with the number of MMAs.  So TMEM only ever holds the sum of one K
-// chunk of 256 (96 MMAs); two TMEM accumulators alternate, and the accumulate
-// warps add each finished chunk into a running sum in registers with
-// round-to-nearest adds while the tensor core already works on the next chunk.
-// The same double buffering hides the epilogue behind the next tile's MMAs.
+// linearly with the number of MMAs.  So a TMEM accumulator only ever holds the
+// sum of one chunk of 8 k blocks (96 MMAs); the accumulate warps add each
+// finished chunk into a running sum in registers with round-to-nearest adds
+// and clear the columns again, so every MMA accumulates (none overwrites).
 //
-// Two MMA issuers.  A tf32 MMA of this shape (128 x 144 x 8) runs for only ~72 cycles and the
-// tensor pipe accepts few instructions ahead, so a single issuing thread leaves the pipe idle
-// whenever it waits on a barrier or commits (measured: ~900 of ~1870 cycles per k block).  Two
-// warps therefore issue alternate k blocks.  To make the order of their MMAs irrelevant every MMA
-// accumulates (none overwrites): the accumulate warps clear a TMEM accumulator after draining it.
+// Two MMA issuers, one accumulator each.  A tf32 MMA of this shape (128 x 144 x 8) runs for only
+// ~72 cycles and the tensor pipe accepts few instructions ahead, so a single issuing thread leaves
+// the pipe idle whenever it waits on a barrier or commits (measured: ~900 of ~1870 cycles per
+// k block).  Two warps therefore issue alternate k blocks: the barrier waits of one overlap the
+// issue of the other.  MMAs issued by different threads are not ordered against one another (two
+// issuers adding into ONE accumulator lost updates once the pipe was saturated), so each issuer owns
+// a TMEM accumulator: the MMAs into one accumulator all come from one thread, in k order, and the
+// result does not depend on timing.  The chunk boundaries of the two accumulators are half a chunk
+// apart, so while one accumulator is drained the other issuer keeps the pipe busy; the same
+// overlap hides the epilogue behind the next tile's MMAs.
 //
 // Pipeline per CTA (persistent, one CTA per SM, 16 warps):
 //   warp 0        TMA producer of the weight ring (W_STAGES x 16 KB, raw FP32)
-//   warp 1, 15    MMA issuers for even / odd k blocks (warp 1 also owns the TMEM allocation); a commit
-//                 per k block frees the token stage and the TMEM weight buffer, a commit per K chunk
-//                 hands the accumulator to the accumulate warps
+//   warp 1, 15    MMA issuers for even / odd k blocks into accumulator 0 / 1 (warp 1 also owns the TMEM
+//                 allocation); a commit per k block frees the token stage and the TMEM weight buffer,
+//                 a commit per chunk hands the issuer's accumulator to the accumulate warps
 //   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and
 //                 every other 16-column slice per warp), add into registers, clear the
 //                 columns; after the last chunk gelu*dot + TF32 split (lane pairs exchange a
 //                 and b by shuffle) or residual add, stores contiguous over the weight-row index
 //   warps 10..13  transform: weight tile shared memory -> registers -> hi/lo -> TMEM
-//   warp 14       TMA producer of the token ring (RING stages x two planes)
+//   warp 14       TMA producer of the token ring (T_STAGES x two planes)
 // TMEM columns: accumulators at 0 and 160, weight head/tail buffers at 320, 384 and 448.
 // Tiles are (expert, 128-row weight block, token chunk); the list is derived in
 // the kernel from offset[E+1], so no host synchronisation is needed.  Every
@@ -134,14 +139,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                            int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -171,17 +168,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Stores 8 consecutive TMEM columns of this thread's lane.
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
 // Clears 16 consecutive TMEM columns of this thread's lane.
 __device__ __forceinline__ void tmem_zero16(uint32_t taddr) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
         "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(0u)
+        : "memory");
+}
+// Stores 32 consecutive TMEM columns of this thread's lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -215,17 +218,16 @@ constexpr int GEMM_THREADS = (MMA2_WARP + 1) * 32;
 constexpr int ACC_STRIDE = 160;                       // TMEM columns between the two accumulators
 constexpr int WBUF_COL = 2 * ACC_STRIDE;              // first TMEM column of the weight head/tail buffers
 constexpr int WBUF_STRIDE = 2 * BK;                   // head (BK columns) then tail (BK columns)
-constexpr int RING = 3;                               // depth of the token ring and of the TMEM weight buffers
+constexpr int WBUFS = 3;                              // TMEM weight head/tail buffers
 constexpr int TMEM_COLS = 512;
-constexpr int K_CHUNK = 256;                          // K extent accumulated inside the tensor core at a time
-constexpr int KB_PER_CHUNK = K_CHUNK / BK;
+constexpr int CHUNK_BLOCKS = 8;                       // k blocks (of 12 MMAs) one accumulator takes between two drains
 constexpr int W_TILE = UMMA_M * ROW_BYTES;            // 16 KB of raw FP32 weights per k block
 
-template <int NMAX, int W_STAGES>
+template <int NMAX, int W_STAGES, int T_STAGES>
 struct Cfg {
     static constexpr int A_TILE = NMAX * ROW_BYTES;                 // one plane of the token tile
     static constexpr int A_STAGE = 2 * A_TILE;
-    static constexpr int SMEM = W_STAGES * W_TILE + RING * A_STAGE + 1024;   // + slack for 1024-byte alignment
+    static constexpr int SMEM = W_STAGES * W_TILE + T_STAGES * A_STAGE + 1024;   // + slack for 1024-byte alignment
     static constexpr int SLICES = NMAX / 32;                        // 16-column slices owned by one epilogue thread
     static_assert(NMAX % 32 == 0 && NMAX <= ACC_STRIDE, "token chunk");
     static_assert(A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
@@ -242,6 +244,14 @@ struct GemmArgs {
     const float* resid;         // RESIDUAL: x [T][M_total]
     int* status;
 };
+
+// True when k block kb (of KB) is the last one of a chunk of its accumulator (accumulator kb & 1 takes
+// every other k block).  Chunks are CHUNK_BLOCKS own blocks long; those of accumulator 1 are shifted by
+// half a chunk so that the two accumulators are never drained at the same time.
+__device__ __forceinline__ bool chunk_ends(int kb, int KB) {
+    const int i = kb & 1, n = kb >> 1;
+    return ((n + 1 + i * (CHUNK_BLOCKS / 2)) % CHUNK_BLOCKS) == 0 || kb + 2 >= KB;
+}
 
 struct TileInfo {
     int expert, slot, mb, row0, n_tok, n_pad;
@@ -275,19 +285,20 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, c
     return t;
 }
 
-template <int EPI, int NMAX, int W_STAGES>
+template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a_hi,
-                const __grid_constant__ CUtensorMap map_a_lo, const GemmArgs args) {
-    using C = Cfg<NMAX, W_STAGES>;
+                const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_hi,
+                const __grid_constant__ CUtensorMap map_b_lo, const GemmArgs args) {
+    using C = Cfg<NMAX, W_STAGES, T_STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_w_full[W_STAGES];    // TMA -> transform
     __shared__ __align__(8) uint64_t s_w_empty[W_STAGES];   // transform -> TMA
-    __shared__ __align__(8) uint64_t s_a_full[RING];        // TMA -> MMA: token stage filled
-    __shared__ __align__(8) uint64_t s_wb_ready[RING];      // transform -> MMA: TMEM weight buffer filled
-    __shared__ __align__(8) uint64_t s_kb_done[RING];       // MMA -> TMA and transform: the k block's MMAs are done,
-                                                            // its token stage and TMEM weight buffer are free
-    __shared__ __align__(8) uint64_t s_acc_full[2];         // both MMA issuers -> accumulate warps
+    __shared__ __align__(8) uint64_t s_a_full[T_STAGES];    // TMA -> MMA: token stage filled
+    __shared__ __align__(8) uint64_t s_a_empty[T_STAGES];   // MMA -> TMA: token stage consumed
+    __shared__ __align__(8) uint64_t s_wb_ready[WBUFS];     // transform -> MMA: TMEM weight buffer filled
+    __shared__ __align__(8) uint64_t s_wb_free[WBUFS];      // MMA -> transform: TMEM weight buffer consumed
+    __shared__ __align__(8) uint64_t s_acc_full[2];         // MMA issuer i -> accumulate warps: chunk of accumulator i done
     __shared__ __align__(8) uint64_t s_acc_empty[2];        // accumulate warps -> MMA: drained and cleared
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -327,13 +338,16 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_init(smem_u32(&s_w_full[s]), 1);
             mbar_init(smem_u32(&s_w_empty[s]), XF_WARPS * 32);
         }
-        for (int s = 0; s < RING; ++s) {
+        for (int s = 0; s < T_STAGES; ++s) {
             mbar_init(smem_u32(&s_a_full[s]), 1);
+            mbar_init(smem_u32(&s_a_empty[s]), 1);
+        }
+        for (int s = 0; s < WBUFS; ++s) {
             mbar_init(smem_u32(&s_wb_ready[s]), XF_WARPS * 32);
-            mbar_init(smem_u32(&s_kb_done[s]), 1);
+            mbar_init(smem_u32(&s_wb_free[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&s_acc_full[b]), 2);
+            mbar_init(smem_u32(&s_acc_full[b]), 1);
             mbar_init(smem_u32(&s_acc_empty[b]), EPI_WARPS * 32);
         }
         s_abort = 0;
@@ -365,7 +379,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     if (!mbar_wait(smem_u32(&s_w_empty[s]), ((it / W_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&s_w_full[s]);
                     mbar_expect_tx(bar, W_TILE);
-                    tma_load_3d(w_ring + s * W_TILE, &map_w, bar, kb * BK, t.mb * UMMA_M, t.slot);
+                    tma_load_2d(w_ring + s * W_TILE, &map_w, bar, 0, ((t.slot * MB + t.mb) * KB + kb) * UMMA_M);
                 }
                 if (!ok) break;
             }
@@ -376,18 +390,26 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+                // few tokens: boxes of 32 rows; otherwise one box of NMAX rows per plane (rows past the
+                // chunk belong to the next expert or are zero-filled past the end; the MMA never reads them)
                 const int nbox = (t.n_pad + 31) >> 5;
-                const uint32_t a_bytes = 2 * nbox * 32 * ROW_BYTES;
+                const bool big = 2 * t.n_pad > NMAX;
+                const uint32_t a_bytes = big ? 2 * C::A_TILE : 2 * nbox * 32 * ROW_BYTES;
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % RING;
-                    if (!mbar_wait(smem_u32(&s_kb_done[s]), ((it / RING) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const int s = it % T_STAGES;
+                    if (!mbar_wait(smem_u32(&s_a_empty[s]), ((it / T_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&s_a_full[s]);
                     mbar_expect_tx(bar, a_bytes);
                     const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
-                    for (int b = 0; b < nbox; ++b) {
-                        tma_load_2d(a_hi + b * 32 * ROW_BYTES, &map_a_hi, bar, kb * BK, t.row0 + b * 32);
-                        tma_load_2d(a_lo + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * BK, t.row0 + b * 32);
+                    if (big) {
+                        tma_load_2d(a_hi, &map_b_hi, bar, kb * BK, t.row0);
+                        tma_load_2d(a_lo, &map_b_lo, bar, kb * BK, t.row0);
+                    } else {
+                        for (int b = 0; b < nbox; ++b) {
+                            tma_load_2d(a_hi + b * 32 * ROW_BYTES, &map_a_hi, bar, kb * BK, t.row0 + b * 32);
+                            tma_load_2d(a_lo + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * BK, t.row0 + b * 32);
+                        }
                     }
                 }
                 if (!ok) break;
@@ -395,69 +417,59 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     } else if (warp == 1 || warp == MMA2_WARP) {
         // ================= MMA issuers =================
-        // Both warps walk every k block; warp 1 issues the even ones, the other warp the odd ones
-        // (by the CTA-wide k block counter).  The whole warp runs the loop so that addresses and
-        // descriptors stay warp-uniform; one lane issues the tcgen05 instructions.  All MMAs
-        // accumulate into an accumulator the accumulate warps have cleared, so the interleaving
-        // of the two issuers does not matter.
+        // Warp 1 issues the even k blocks of every tile into accumulator 0, the other warp the odd
+        // ones into accumulator 1.  The whole warp runs the loop so that addresses and descriptors
+        // stay warp-uniform; one lane issues the tcgen05 instructions.
         const uint32_t mine = warp == 1 ? 0u : 1u;
         const bool leader = lane == 0;
-        uint32_t it = 0, chunk = 0;
+        const uint32_t d = tmem_base + mine * ACC_STRIDE;
+        const uint32_t acc_empty = smem_u32(&s_acc_empty[mine]), acc_full = smem_u32(&s_acc_full[mine]);
+        uint32_t it = 0, rounds = 0;   // rounds: hand-overs of this issuer's accumulator so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
             const uint32_t idesc = make_idesc(t.n_pad);
-            bool ok = true, entered = false;   // entered: this warp has already waited for the chunk's accumulator
+            bool ok = true, entered = false;   // entered: the accumulator has been taken over for the current chunk
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                const int kc = kb % KB_PER_CHUNK;
-                const uint32_t buf = chunk & 1;
-                if (kc == 0) entered = false;
-                if ((it & 1u) == mine) {
-                    if (!entered) {  // the accumulator of this chunk must have been drained and cleared
-                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
-                        entered = true;
-                    }
-                    const int s = it % RING;
-                    const uint32_t ph = (it / RING) & 1;
-                    if (!mbar_wait(smem_u32(&s_a_full[s]), ph, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(smem_u32(&s_wb_ready[s]), ph, abort_flag)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
-                    const uint32_t d = tmem_base + buf * ACC_STRIDE;
-                    const uint32_t w_hi = tmem_base + WBUF_COL + s * WBUF_STRIDE, w_lo = w_hi + BK;
-                    const uint64_t d_a_hi = make_smem_desc(a_hi), d_a_lo = make_smem_desc(a_lo);
-                    if (leader) {
-#pragma unroll
-                        for (int ks = 0; ks < BK / 8; ++ks) {
-                            // 8 TF32 = 32 bytes along K inside the swizzled row = 2 units of the descriptor address
-                            const uint64_t b_hi = d_a_hi + 2 * ks, b_lo = d_a_lo + 2 * ks;
-                            umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, 1u);   // small terms first
-                            umma_tf32_ts(d, w_hi + ks * 8, b_lo, idesc, 1u);
-                            umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
-                        }
-                        // token stage and TMEM weight buffer are free once these MMAs have completed
-                        umma_commit(smem_u32(&s_kb_done[s]));
-                    }
+                if ((uint32_t)(kb & 1) != mine) continue;
+                if (!entered) {  // the accumulator must have been drained and cleared
+                    if (!mbar_wait(acc_empty, rounds & 1, abort_flag)) { ok = false; break; }
+                    entered = true;
                 }
-                if (kc == KB_PER_CHUNK - 1 || kb == KB - 1) {
-                    // chunk complete for this issuer: its MMAs of the chunk (if any) gate the hand-over
-                    if (!entered) {
-                        // nothing of this chunk was issued here (a one-block tail chunk); still wait for the
-                        // accumulator's previous round to be over so that this arrival counts for the right phase
-                        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
-                        if (leader) mbar_arrive(smem_u32(&s_acc_full[buf]));
-                    } else if (leader) {
-                        umma_commit(smem_u32(&s_acc_full[buf]));
+                const int s = it % T_STAGES;
+                const uint32_t wb = it % WBUFS;
+                if (!mbar_wait(smem_u32(&s_a_full[s]), (it / T_STAGES) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&s_wb_ready[wb]), (it / WBUFS) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
+                    const uint32_t w_hi = tmem_base + WBUF_COL + wb * WBUF_STRIDE, w_lo = w_hi + BK;
+                    const uint64_t d_a_hi = make_smem_desc(a_hi), d_a_lo = make_smem_desc(a_lo);
+#pragma unroll
+                    for (int ks = 0; ks < BK / 8; ++ks) {
+                        // 8 TF32 = 32 bytes along K inside the swizzled row = 2 units of the descriptor address
+                        const uint64_t b_hi = d_a_hi + 2 * ks, b_lo = d_a_lo + 2 * ks;
+                        umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, 1u);   // small terms first
+                        umma_tf32_ts(d, w_hi + ks * 8, b_lo, idesc, 1u);
+                        umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
                     }
-                    ++chunk;
+                    // token stage and TMEM weight buffer are free once these MMAs have completed
+                    umma_commit(smem_u32(&s_a_empty[s]));
+                    umma_commit(smem_u32(&s_wb_free[wb]));
+                    if (chunk_ends(kb, KB)) umma_commit(acc_full);
+                }
+                if (chunk_ends(kb, KB)) {
+                    ++rounds;
+                    entered = false;
                 }
             }
             if (!ok) break;
         }
     } else if (warp < 2 + EPI_WARPS) {
         // ================= accumulate + epilogue (warps 2..9) =================
-        // Each K chunk is accumulated in TMEM from a cleared accumulator and added here, with
+        // Each chunk is accumulated in TMEM from a cleared accumulator and added here, with
         // round-to-nearest adds, to a running sum in registers; the columns are cleared again
-        // before the accumulator goes back to the MMA issuers.
+        // before the accumulator goes back to its MMA issuer.  The chunks of the two accumulators
+        // are taken in the fixed order of their last k block.
         const int q = warp & 3;                 // TMEM lane quarter this warp may access
         const int half = (warp - 2) >> 2;       // even or odd 16-column slices
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -471,8 +483,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         tc_fence_before();
         mbar_arrive(smem_u32(&s_acc_empty[0]));
         mbar_arrive(smem_u32(&s_acc_empty[1]));
-        uint32_t chunk = 0;
-        const int NC = (KB + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
+        uint32_t rounds0 = 0, rounds1 = 0;      // hand-overs of accumulator 0 / 1 so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
             const int nsl = t.n_pad >> 4;
@@ -482,9 +493,12 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < 16; ++c) sum[i][c] = 0.f;
             bool ok = true;
-            for (int ch = 0; ch < NC; ++ch, ++chunk) {
-                const uint32_t buf = chunk & 1;
-                if (!mbar_wait(smem_u32(&s_acc_full[buf]), (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
+            for (int kb = 0; kb < KB; ++kb) {
+                if (!chunk_ends(kb, KB)) continue;
+                const uint32_t buf = kb & 1;
+                const uint32_t par = (buf ? rounds1 : rounds0) & 1;
+                if (buf) ++rounds1; else ++rounds0;
+                if (!mbar_wait(smem_u32(&s_acc_full[buf]), par, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int i = 0; i < C::SLICES; ++i) {
@@ -541,41 +555,47 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int r = q * 32 + lane;
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + WBUF_COL;
         const uint8_t* w_ring_ptr = smem_raw + (w_ring - smem_u32(smem_raw));
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-            bool ok = true;
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-                const int s = it % W_STAGES;
-                const uint32_t wb = it % RING;
-                if (!mbar_wait(smem_u32(&s_w_full[s]), (it / W_STAGES) & 1, abort_flag)) { ok = false; break; }
-                const uint8_t* row = w_ring_ptr + s * W_TILE + r * ROW_BYTES;
-                float4 v[8];
+        // Software pipeline: while the TMEM stores of k block `it` are in flight, the tile of k block
+        // it + 1 is already read from shared memory (and its slot handed back to the producer).
+        int my_tiles = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) ++my_tiles;
+        const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)KB;
+        float4 v[8];
+        bool ok = total_it > 0 && !*abort_flag;
+        auto fetch = [&](uint32_t it) -> bool {
+            const int s = it % W_STAGES;
+            if (!mbar_wait(smem_u32(&s_w_full[s]), (it / W_STAGES) & 1, abort_flag)) return false;
+            const uint8_t* row = w_ring_ptr + s * W_TILE + r * ROW_BYTES;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
-                mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
-                // the MMAs that read this TMEM buffer RING k blocks ago must be done
-                if (!mbar_wait(smem_u32(&s_kb_done[wb]), ((it / RING) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t dst = tlane + wb * WBUF_STRIDE;
+            for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
+            mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
+            return true;
+        };
+        if (ok) ok = fetch(0);
+        for (uint32_t it = 0; ok && it < total_it; ++it) {
+            const uint32_t wb = it % WBUFS;
+            uint32_t hi[32], lo[32];
 #pragma unroll
-                for (int c = 0; c < 8; c += 2) {
-                    uint32_t hi[8], lo[8];
-                    const float x[8] = {v[c].x, v[c].y, v[c].z, v[c].w, v[c + 1].x, v[c + 1].y, v[c + 1].z, v[c + 1].w};
+            for (int c = 0; c < 8; ++c) {
+                const float x[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float h, l;
-                        split_tf32(x[j], h, l);
-                        hi[j] = __float_as_uint(h);
-                        lo[j] = __float_as_uint(l);
-                    }
-                    tmem_st8(dst + c * 4, hi);
-                    tmem_st8(dst + BK + c * 4, lo);
+                for (int j = 0; j < 4; ++j) {
+                    float h, l;
+                    split_tf32(x[j], h, l);
+                    hi[4 * c + j] = __float_as_uint(h);
+                    lo[4 * c + j] = __float_as_uint(l);
                 }
-                tmem_st_wait();
-                tc_fence_before();
-                mbar_arrive(smem_u32(&s_wb_ready[wb]));
             }
-            if (!ok) break;
+            // the MMAs that read this TMEM buffer WBUFS k blocks ago must be done
+            if (!mbar_wait(smem_u32(&s_wb_free[wb]), ((it / WBUFS) & 1) ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t dst = tlane + wb * WBUF_STRIDE;
+            tmem_st32(dst, hi);
+            tmem_st32(dst + BK, lo);
+            if (it + 1 < total_it) ok = fetch(it + 1);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&s_wb_ready[wb]));
         }
     }
 
@@ -637,18 +657,22 @@ int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uin
     return INFMOE_OK;
 }
 
-template <int EPI, int NMAX, int W_STAGES>
+template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
 int launch_one(const GemmArgs& args, long long T, int slots, const float* w, const float* a_hi, const float* a_lo,
                int num_ctas, cudaStream_t stream) {
-    using C = Cfg<NMAX, W_STAGES>;
+    using C = Cfg<NMAX, W_STAGES, T_STAGES>;
     static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory rings too large");
-    CUtensorMap m[3];
-    INFMOE_TRY(make_map(&m[0], w, args.K, args.M_total, slots, UMMA_M, 3));
+    CUtensorMap m[5];
+    // weights: tile-contiguous plane = a [slots * MB * KB * 128][32] matrix, one 16 KB tile per box
+    const uint64_t w_rows = (uint64_t)slots * ((args.M_total + UMMA_M - 1) / UMMA_M) * ((args.K + BK - 1) / BK) * UMMA_M;
+    INFMOE_TRY(make_map(&m[0], w, BK, w_rows, 1, UMMA_M, 2));
     INFMOE_TRY(make_map(&m[1], a_hi, args.K, (uint64_t)T, 1, 32, 2));
     INFMOE_TRY(make_map(&m[2], a_lo, args.K, (uint64_t)T, 1, 32, 2));
-    auto kern = ffn_umma_kernel<EPI, NMAX, W_STAGES>;
+    INFMOE_TRY(make_map(&m[3], a_hi, args.K, (uint64_t)T, 1, NMAX, 2));
+    INFMOE_TRY(make_map(&m[4], a_lo, args.K, (uint64_t)T, 1, NMAX, 2));
+    auto kern = ffn_umma_kernel<EPI, NMAX, W_STAGES, T_STAGES>;
     INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], args);
+    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], m[4], args);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -662,7 +686,9 @@ bool ffn_umma_supported(int D, int F, int E) {
 
 // Grouped FFN over experts [e_begin, e_end); T rows in expert-contiguous order.
 //   h_hi/h_lo [T][D], g_hi/g_lo [T][F] (scratch), routed [T][D], post [T][D]
-//   w01 [slots][2F][D] raw FP32: row 2f = wi_0[f], row 2f+1 = wi_1[f];  wo [slots][D][F] raw FP32
+//   w01 [slots] x tiled(2F x D) raw FP32: row 2f = wi_0[f], row 2f+1 = wi_1[f];  wo [slots] x tiled(D x F);
+//   tiled = 128 x 32 tiles stored contiguously (launch_retile), so a CTA streams its weights as one
+//   sequential run of 16 KB tiles
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
                     const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
                     const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
@@ -690,22 +716,23 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a2.out_hi = post;
     a2.out_lo = nullptr;
     a2.resid = routed;
-    // Shapes: token chunk, weight stages (16 KB each).  INFMOE_GEMM_TILE selects another instantiation
+    // Shapes: token chunk, weight stages (16 KB each), token stages.  INFMOE_GEMM_TILE selects another instantiation
     // for tuning runs.
     static const int variant = [] {
         const char* v = getenv("INFMOE_GEMM_TILE");
         return v ? atoi(v) : 0;
     }();
-#define INFMOE_LAUNCH_PAIR(NMAX, WS)                                                                         \
-    do {                                                                                                      \
-        INFMOE_TRY((launch_one<EPI_GELU_PAIR, NMAX, WS>(a1, T, slots, w01, h_hi, h_lo, num_sms, stream)));    \
-        if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));                                   \
-        INFMOE_TRY((launch_one<EPI_RESIDUAL, NMAX, WS>(a2, T, slots, wo, g_hi, g_lo, num_sms, stream)));      \
+#define INFMOE_LAUNCH_PAIR(NMAX, WS, TS)                                                                         \
+    do {                                                                                                          \
+        INFMOE_TRY((launch_one<EPI_GELU_PAIR, NMAX, WS, TS>(a1, T, slots, w01, h_hi, h_lo, num_sms, stream)));    \
+        if (mid_event) INFMOE_CUDA_TRY(cudaEventRecord(mid_event, stream));                                       \
+        INFMOE_TRY((launch_one<EPI_RESIDUAL, NMAX, WS, TS>(a2, T, slots, wo, g_hi, g_lo, num_sms, stream)));      \
     } while (0)
     switch (variant) {
-        case 1: INFMOE_LAUNCH_PAIR(160, 3); break;
-        case 2: INFMOE_LAUNCH_PAIR(128, 6); break;
-        default: INFMOE_LAUNCH_PAIR(160, 5); break;
+        case 1: INFMOE_LAUNCH_PAIR(160, 3, 4); break;
+        case 2: INFMOE_LAUNCH_PAIR(160, 6, 3); break;
+        case 3: INFMOE_LAUNCH_PAIR(128, 3, 5); break;
+        default: INFMOE_LAUNCH_PAIR(160, 5, 3); break;
     }
 #undef INFMOE_LAUNCH_PAIR
     return INFMOE_OK;

@@ -24,11 +24,14 @@ int launch_mix_gather(long long T, int D, const int* pos, const float* routed, c
 int launch_layernorm(float* out, const float* in, long long n, int D, const float* gamma, cudaStream_t stream);
 int launch_gelu_dot(const float* a, float* b, size_t len, cudaStream_t stream);
 int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_t stream);
+// Tile-contiguous weight layout (see rows.cu); src1 != NULL interleaves the rows of two matrices.
+int launch_retile(const float* src0, const float* src1, int M, int K, float* dst, cudaStream_t stream);
+inline size_t tiled_elems(int M, int K) { return (size_t)((M + 127) / 128) * 128 * (size_t)((K + 31) / 32) * 32; }
 int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
                     cudaStream_t stream);
 
-// Expert weights live in two raw FP32 planes: w01 [slots][2F][D] (row 2f = wi_0[f], row 2f+1 = wi_1[f]) and
-// wo [slots][D][F].  Activations travel as TF32 head/tail planes (hi = value rounded to TF32, lo = value - hi).
+// Expert weights live in two raw FP32 planes in tile-contiguous layout (128 x 32 tiles, see launch_retile):
+// w01 [slots] x tiled(2F x D) (row 2f = wi_0[f], row 2f+1 = wi_1[f]) and wo [slots] x tiled(D x F).  Activations travel as TF32 head/tail planes (hi = value rounded to TF32, lo = value - hi).
 int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
                     const float* h_hi, const float* h_lo, const float* w01, const float* wo, const float* routed,
                     float* g_hi, float* g_lo, float* post, cudaStream_t stream);

@@ -63,16 +63,17 @@ struct ExpertStore {
     // device: LayerNorm weights of all experts [E][D] (always resident, 4*E*D bytes)
     float* d_ln = nullptr;
     std::vector<char> ln_on_device;
-    // device-resident raw FP32 weights:
-    //   [0] w01 [E][2F][D]  (row 2f = wi_0[f], row 2f+1 = wi_1[f])
-    //   [1] wo  [E][D][F]
+    // device-resident raw FP32 weights in the GEMM's tile-contiguous layout (launch_retile):
+    //   [0] w01 [E] x tiled(2F x D)  (row 2f = wi_0[f], row 2f+1 = wi_1[f])
+    //   [1] wo  [E] x tiled(D x F)
     float* d_plane[2] = {nullptr, nullptr};
+    float* d_staging = nullptr;   // 3*D*F floats: landing area of host weights before they are retiled
     std::vector<char> on_device;
     bool fortran_warning = false;
 
     size_t matrix_elems() const { return (size_t)D * (size_t)F; }
-    size_t plane_elems(int p) const { return (p == 0 ? 2 : 1) * matrix_elems(); }   // per expert
-    size_t resident_bytes() const { return 3 * matrix_elems() * (size_t)E * sizeof(float); }
+    size_t plane_elems(int p) const { return p == 0 ? tiled_elems(2 * F, D) : tiled_elems(D, F); }   // per expert
+    size_t resident_bytes() const { return (plane_elems(0) + plane_elems(1)) * (size_t)E * sizeof(float); }
 
     ~ExpertStore() {
         for (auto& v : {&h_ln, &h_wi0, &h_wi1, &h_wo})
@@ -81,6 +82,7 @@ struct ExpertStore {
         if (d_ln) cudaFree(d_ln);
         for (float* p : d_plane)
             if (p) cudaFree(p);
+        if (d_staging) cudaFree(d_staging);
     }
 };
 
@@ -182,7 +184,9 @@ WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     w.h_lo = take(4 * t * D);
     w.g_hi = take(4 * t * F);
     w.g_lo = take(4 * t * F);
-    w.slots = take(streamed && !L->identity ? 3 * (size_t)L->mc * D * F * 4 : 0);
+    w.slots = take(streamed && !L->identity
+                       ? 4 * (size_t)L->mc * (tiled_elems(2 * L->F, L->D) + tiled_elems(L->D, L->F) + 3 * D * F)
+                       : 0);
     w.total = o;
     return w;
 }
@@ -210,25 +214,38 @@ int ensure_resident_planes(ExpertStore* s) {
     return INFMOE_OK;
 }
 
-// Puts one expert's matrices into its two planes: wi_0 / wi_1 rows interleaved into w01 by two strided
-// copies, wo as it is.  The weights stay raw FP32 (the GEMM kernel splits them on the fly).
+// Puts one expert's matrices into its two planes (tile-contiguous, wi_0 / wi_1 rows interleaved).  Host
+// sources first land in `staging` (device, 3*D*F floats); the weights stay raw FP32 (the GEMM kernel splits
+// them into TF32 head and tail on the fly).
 int load_expert_planes(int D, int F, const float* wi0, const float* wi1, const float* wo, float* w01, float* wo_dst,
-                       cudaMemcpyKind kind, cudaStream_t stream) {
-    const size_t row = sizeof(float) * (size_t)D;
-    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01, 2 * row, wi0, row, row, (size_t)F, kind, stream));
-    INFMOE_CUDA_TRY(cudaMemcpy2DAsync(w01 + D, 2 * row, wi1, row, row, (size_t)F, kind, stream));
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(wo_dst, wo, sizeof(float) * (size_t)D * F, kind, stream));
+                       bool src_on_host, float* staging, cudaStream_t stream) {
+    const size_t n = (size_t)D * F;
+    if (src_on_host) {
+        if (!staging) {
+            set_error("load_expert_planes: no staging buffer for host weights");
+            return INFMOE_ERR_STATE;
+        }
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(staging, wi0, sizeof(float) * n, cudaMemcpyHostToDevice, stream));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(staging + n, wi1, sizeof(float) * n, cudaMemcpyHostToDevice, stream));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(staging + 2 * n, wo, sizeof(float) * n, cudaMemcpyHostToDevice, stream));
+        wi0 = staging;
+        wi1 = staging + n;
+        wo = staging + 2 * n;
+    }
+    INFMOE_TRY(launch_retile(wi0, wi1, 2 * F, D, w01, stream));
+    INFMOE_TRY(launch_retile(wo, nullptr, D, F, wo_dst, stream));
     return INFMOE_OK;
 }
 
 // Uploads every expert that is on the host but not yet on the device.
 int upload_resident(ExpertStore* s, cudaStream_t stream) {
     INFMOE_TRY(ensure_resident_planes(s));
-    const size_t n = s->matrix_elems();
     for (int e = 0; e < s->E; ++e) {
         if (s->on_device[e] || !s->on_host[e]) continue;
-        INFMOE_TRY(load_expert_planes(s->D, s->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e], s->d_plane[0] + 2 * n * e,
-                                      s->d_plane[1] + n * e, cudaMemcpyHostToDevice, stream));
+        if (!s->d_staging) INFMOE_CUDA_TRY(cudaMalloc(&s->d_staging, sizeof(float) * 3 * s->matrix_elems()));
+        INFMOE_TRY(load_expert_planes(s->D, s->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e],
+                                      s->d_plane[0] + s->plane_elems(0) * e, s->d_plane[1] + s->plane_elems(1) * e,
+                                      true, s->d_staging, stream));
         s->on_device[e] = 1;
     }
     return INFMOE_OK;
@@ -549,8 +566,8 @@ int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const
         INFMOE_TRY(ensure_resident_planes(s));
         INFMOE_CUDA_TRY(cudaMemcpy(s->d_ln + (size_t)e * s->D, ln_w, sizeof(float) * s->D, cudaMemcpyDeviceToDevice));
         s->ln_on_device[e] = 1;
-        INFMOE_TRY(load_expert_planes(s->D, s->F, wi0, wi1, wo, s->d_plane[0] + 2 * n * e, s->d_plane[1] + n * e,
-                                      cudaMemcpyDeviceToDevice, 0));
+        INFMOE_TRY(load_expert_planes(s->D, s->F, wi0, wi1, wo, s->d_plane[0] + s->plane_elems(0) * e,
+                                      s->d_plane[1] + s->plane_elems(1) * e, false, nullptr, 0));
         INFMOE_CUDA_TRY(cudaStreamSynchronize(0));
         s->on_device[e] = 1;
     } else {
@@ -680,10 +697,12 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                                stream, mid));
         } else {
             const size_t n = s->matrix_elems();
-            // slot planes: w01 [mc][2F][D], then wo [mc][D][F]
+            // slot planes: w01 [mc] x tiled(2F x D), wo [mc] x tiled(D x F), then one raw landing area per slot
+            const size_t n0 = s->plane_elems(0), n1 = s->plane_elems(1);
             float* planes[2];
             planes[0] = (float*)(base + w.slots);
-            planes[1] = planes[0] + 2 * n * L->mc;
+            planes[1] = planes[0] + n0 * L->mc;
+            float* staging = planes[1] + n1 * L->mc;
             // the one host synchronisation of the streamed path: which experts have rows?
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_count, count, sizeof(int) * L->E, cudaMemcpyDeviceToHost, stream));
             INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
@@ -712,9 +731,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                 cudaStream_t cs = L->copy_streams[j % L->copy_streams.size()];
                 // the slot is free once the expert that used it (j - mc) has run
                 if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
-                INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e],
-                                              planes[0] + 2 * n * slot, planes[1] + n * slot, cudaMemcpyHostToDevice,
-                                              cs));
+                INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e], planes[0] + n0 * slot,
+                                              planes[1] + n1 * slot, true, staging + 3 * n * slot, cs));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
                 INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
                 INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, L->mc, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
@@ -1081,8 +1099,8 @@ int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* byte
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + align_up(8 * d * f) + align_up(4 * d * f) +
-             2 * ALIGN + ALIGN;
+    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + align_up(4 * tiled_elems(2 * F, D)) +
+             align_up(4 * tiled_elems(D, F)) + 2 * ALIGN + ALIGN;
     return INFMOE_OK;
 }
 
@@ -1112,15 +1130,15 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
     float* g_hi = (float*)take(4 * r * f);
     float* g_lo = (float*)take(4 * r * f);
     float* planes[2];
-    planes[0] = (float*)take(8 * d * f);
-    planes[1] = (float*)take(4 * d * f);
+    planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
+    planes[1] = (float*)take(4 * tiled_elems(D, F));
     int* offset = (int*)take(8);
     int* status = (int*)take(4);
     const int h_offset[2] = {0, (int)rows};
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], cudaMemcpyDeviceToDevice, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -1226,8 +1244,8 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     float* g_hi = (float*)take(4 * r * f);
     float* g_lo = (float*)take(4 * r * f);
     float* planes[2];
-    planes[0] = (float*)take(8 * d * f);
-    planes[1] = (float*)take(4 * d * f);
+    planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
+    planes[1] = (float*)take(4 * tiled_elems(D, F));
     int* offset = (int*)take(8);
     int* status = (int*)take(4);
     // The array keeps whatever the previous call left: everything read below is rewritten first
@@ -1236,7 +1254,7 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], cudaMemcpyDeviceToDevice, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

@@ -187,6 +187,29 @@ __global__ void split_kernel(const float* __restrict__ src, float* __restrict__ 
         split_tf32(src[i], hi[i], lo[i]);
 }
 
+// Weight matrix -> tile-contiguous layout for the tensor-core GEMM: tiles of 128 rows x 32 floats (16 KB),
+// tile (mb, kb) at ((mb * KB + kb) * 128 rows; rows and columns past the matrix are zero.  With two sources
+// the rows are interleaved: row 2f = src0[f], row 2f+1 = src1[f] (wi_0 / wi_1).  One warp moves one 128-byte
+// row segment, so both the read and the write are coalesced.
+__global__ void __launch_bounds__(256)
+retile_kernel(const float* __restrict__ src0, const float* __restrict__ src1, int M, int K, int MB, int KB,
+              float* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const long long seg = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);   // (mb, kb, r) flattened
+    const long long total = (long long)MB * KB * 128;
+    if (seg >= total) return;
+    const int r = (int)(seg % 128);
+    const long long tile = seg / 128;
+    const int kb = (int)(tile % KB), mb = (int)(tile / KB);
+    const int m = mb * 128 + r, k = kb * 32 + lane;
+    float v = 0.f;
+    if (m < M && k < K) {
+        if (src1) v = (m & 1) ? src1[(size_t)(m >> 1) * K + k] : src0[(size_t)(m >> 1) * K + k];
+        else v = src0[(size_t)m * K + k];
+    }
+    dst[seg * 32 + lane] = v;
+}
+
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 inline unsigned row_grid(long long rows) { return (unsigned)((rows + ROW_WARPS - 1) / ROW_WARPS); }
 
@@ -264,6 +287,15 @@ int launch_ln_split(long long n, int D, const float* in, const float* gamma, flo
     if (n == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(in) && aligned16(gamma);
     ln_split_kernel<<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, h_hi, h_lo);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+int launch_retile(const float* src0, const float* src1, int M, int K, float* dst, cudaStream_t stream) {
+    const int MB = (M + 127) / 128, KB = (K + 31) / 32;
+    const long long segs = (long long)MB * KB * 128;
+    retile_kernel<<<(unsigned)((segs + 7) / 8), 256, 0, stream>>>(src0, src1, M, K, MB, KB, dst);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
