@@ -37,6 +37,10 @@ sys.path.insert(0, ROOT)
 
 from infmoe_b200 import synth  # noqa: E402
 
+# DRAM bytes the wi_0/wi_1 GEMM moves per weight element (ncu capture summarised under profiles/; 4 = each raw
+# FP32 weight crosses HBM once)
+TRAFFIC_BYTES_PER_WEIGHT = 4.2
+
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -278,11 +282,10 @@ def run_single(args, w):
     roofline = None
     if g1_ms:
         achieved = useful_flops / (g1_ms * 1e-3) / 1e12
-        weight_bytes = 2.0 * (2 * D * F * 4) * active  # head + tail planes of the interleaved wi_0/wi_1 matrix
-        # DRAM bytes per launch from the ncu capture of workload cpm2_profile (profiles/): 2.778 GB for 8 experts x
-        # 10240 interleaved weight rows x 4096 floats = 8.28 bytes per weight element (8 algorithmic), scaled by
-        # the weight elements this launch streams.
-        traffic = 8.28 * active * 2.0 * F * D if not w.streamed else None
+        weight_bytes = (2 * D * F * 4.0) * active      # raw FP32 interleaved wi_0/wi_1 matrix of every active expert
+        # DRAM bytes per launch from the ncu capture of workload cpm2_profile (profiles/), expressed per weight
+        # element (4 algorithmic) and scaled by the weight elements this launch streams.
+        traffic = TRAFFIC_BYTES_PER_WEIGHT * active * 2.0 * F * D if not w.streamed else None
         roofline = {"kernel": "ffn_umma_kernel<EPI_GELU_PAIR>", "bound": "tensor", "achieved": achieved,
                     "peak": peak_3xtf32, "unit": "TFLOP/s", "frac": achieved / peak_3xtf32, "traffic": traffic,
                     "peak_source": f"bf16 sustained {peaks['bf16_sustained']} TFLOP/s of {peaks['source']} / 6 "

@@ -219,6 +219,11 @@ constexpr int ACC_STRIDE = 160;                       // TMEM columns between th
 constexpr int WBUF_COL = 2 * ACC_STRIDE;              // first TMEM column of the weight head/tail buffers
 constexpr int WBUF_STRIDE = 2 * BK;                   // head (BK columns) then tail (BK columns)
 constexpr int WBUFS = 3;                              // TMEM weight head/tail buffers
+// A ring of n buffers whose consecutive uses alternate between the two MMA issuers needs one barrier per
+// (buffer, issuer) pair, so that each issuer observes every phase of the barriers it waits on: a waiter
+// that skips phases of a shared barrier can take a stale completion for its own.
+constexpr int barrier_period(int n) { return n % 2 ? 2 * n : n; }
+constexpr int PW = barrier_period(WBUFS);
 constexpr int TMEM_COLS = 512;
 constexpr int CHUNK_BLOCKS = 8;                       // k blocks (of 12 MMAs) one accumulator takes between two drains
 constexpr int W_TILE = UMMA_M * ROW_BYTES;            // 16 KB of raw FP32 weights per k block
@@ -228,6 +233,7 @@ struct Cfg {
     static constexpr int A_TILE = NMAX * ROW_BYTES;                 // one plane of the token tile
     static constexpr int A_STAGE = 2 * A_TILE;
     static constexpr int SMEM = W_STAGES * W_TILE + T_STAGES * A_STAGE + 1024;   // + slack for 1024-byte alignment
+    static constexpr int PA = barrier_period(T_STAGES);             // barriers of the token ring
     static constexpr int SLICES = NMAX / 32;                        // 16-column slices owned by one epilogue thread
     static_assert(NMAX % 32 == 0 && NMAX <= ACC_STRIDE, "token chunk");
     static_assert(A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
@@ -245,9 +251,9 @@ struct GemmArgs {
     int* status;
 };
 
-// True when k block kb (of KB) is the last one of a chunk of its accumulator (accumulator kb & 1 takes
-// every other k block).  Chunks are CHUNK_BLOCKS own blocks long; those of accumulator 1 are shifted by
-// half a chunk so that the two accumulators are never drained at the same time.
+// True when k block kb (of KB) of a tile is the last one of a chunk of its accumulator (each accumulator
+// takes every other k block).  Chunks are CHUNK_BLOCKS own blocks long; those of the odd k blocks are shifted
+// by half a chunk so that the two accumulators are not drained at the same time.
 __device__ __forceinline__ bool chunk_ends(int kb, int KB) {
     const int i = kb & 1, n = kb >> 1;
     return ((n + 1 + i * (CHUNK_BLOCKS / 2)) % CHUNK_BLOCKS) == 0 || kb + 2 >= KB;
@@ -294,10 +300,12 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_w_full[W_STAGES];    // TMA -> transform
     __shared__ __align__(8) uint64_t s_w_empty[W_STAGES];   // transform -> TMA
-    __shared__ __align__(8) uint64_t s_a_full[T_STAGES];    // TMA -> MMA: token stage filled
-    __shared__ __align__(8) uint64_t s_a_empty[T_STAGES];   // MMA -> TMA: token stage consumed
-    __shared__ __align__(8) uint64_t s_wb_ready[WBUFS];     // transform -> MMA: TMEM weight buffer filled
-    __shared__ __align__(8) uint64_t s_wb_free[WBUFS];      // MMA -> transform: TMEM weight buffer consumed
+    // k block `it` (counted over all tiles of the CTA) uses token stage it % T_STAGES with barrier it % PA, and
+    // TMEM weight buffer it % WBUFS with barrier it % PW; it is issued by MMA issuer it & 1
+    __shared__ __align__(8) uint64_t s_a_full[C::PA];       // TMA -> MMA: token stage filled
+    __shared__ __align__(8) uint64_t s_a_empty[C::PA];      // MMA -> TMA: token stage consumed
+    __shared__ __align__(8) uint64_t s_wb_ready[PW];        // transform -> MMA: TMEM weight buffer filled
+    __shared__ __align__(8) uint64_t s_wb_free[PW];         // MMA -> transform: TMEM weight buffer consumed
     __shared__ __align__(8) uint64_t s_acc_full[2];         // MMA issuer i -> accumulate warps: chunk of accumulator i done
     __shared__ __align__(8) uint64_t s_acc_empty[2];        // accumulate warps -> MMA: drained and cleared
     __shared__ uint32_t s_tmem_base;
@@ -338,11 +346,11 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_init(smem_u32(&s_w_full[s]), 1);
             mbar_init(smem_u32(&s_w_empty[s]), XF_WARPS * 32);
         }
-        for (int s = 0; s < T_STAGES; ++s) {
+        for (int s = 0; s < C::PA; ++s) {
             mbar_init(smem_u32(&s_a_full[s]), 1);
             mbar_init(smem_u32(&s_a_empty[s]), 1);
         }
-        for (int s = 0; s < WBUFS; ++s) {
+        for (int s = 0; s < PW; ++s) {
             mbar_init(smem_u32(&s_wb_ready[s]), XF_WARPS * 32);
             mbar_init(smem_u32(&s_wb_free[s]), 1);
         }
@@ -398,8 +406,11 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % T_STAGES;
-                    if (!mbar_wait(smem_u32(&s_a_empty[s]), ((it / T_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    const uint32_t bar = smem_u32(&s_a_full[s]);
+                    if (it >= (uint32_t)T_STAGES) {   // the stage's previous k block must have been consumed
+                        const uint32_t prev = it - T_STAGES;
+                        if (!mbar_wait(smem_u32(&s_a_empty[prev % C::PA]), (prev / C::PA) & 1, abort_flag)) { ok = false; break; }
+                    }
+                    const uint32_t bar = smem_u32(&s_a_full[it % C::PA]);
                     mbar_expect_tx(bar, a_bytes);
                     const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
                     if (big) {
@@ -417,9 +428,9 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     } else if (warp == 1 || warp == MMA2_WARP) {
         // ================= MMA issuers =================
-        // Warp 1 issues the even k blocks of every tile into accumulator 0, the other warp the odd
-        // ones into accumulator 1.  The whole warp runs the loop so that addresses and descriptors
-        // stay warp-uniform; one lane issues the tcgen05 instructions.
+        // Warp 1 issues the even k blocks (counted over all tiles of the CTA) into accumulator 0, the
+        // other warp the odd ones into accumulator 1.  The whole warp runs the loop so that addresses
+        // and descriptors stay warp-uniform; one lane issues the tcgen05 instructions.
         const uint32_t mine = warp == 1 ? 0u : 1u;
         const bool leader = lane == 0;
         const uint32_t d = tmem_base + mine * ACC_STRIDE;
@@ -430,15 +441,15 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const uint32_t idesc = make_idesc(t.n_pad);
             bool ok = true, entered = false;   // entered: the accumulator has been taken over for the current chunk
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                if ((uint32_t)(kb & 1) != mine) continue;
+                if ((it & 1u) != mine) continue;
                 if (!entered) {  // the accumulator must have been drained and cleared
                     if (!mbar_wait(acc_empty, rounds & 1, abort_flag)) { ok = false; break; }
                     entered = true;
                 }
                 const int s = it % T_STAGES;
                 const uint32_t wb = it % WBUFS;
-                if (!mbar_wait(smem_u32(&s_a_full[s]), (it / T_STAGES) & 1, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&s_wb_ready[wb]), (it / WBUFS) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&s_a_full[it % C::PA]), (it / C::PA) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&s_wb_ready[it % PW]), (it / PW) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 if (leader) {
                     const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
@@ -453,8 +464,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
                     }
                     // token stage and TMEM weight buffer are free once these MMAs have completed
-                    umma_commit(smem_u32(&s_a_empty[s]));
-                    umma_commit(smem_u32(&s_wb_free[wb]));
+                    umma_commit(smem_u32(&s_a_empty[it % C::PA]));
+                    umma_commit(smem_u32(&s_wb_free[it % PW]));
                     if (chunk_ends(kb, KB)) umma_commit(acc_full);
                 }
                 if (chunk_ends(kb, KB)) {
@@ -483,7 +494,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         tc_fence_before();
         mbar_arrive(smem_u32(&s_acc_empty[0]));
         mbar_arrive(smem_u32(&s_acc_empty[1]));
-        uint32_t rounds0 = 0, rounds1 = 0;      // hand-overs of accumulator 0 / 1 so far
+        uint32_t it = 0, rounds0 = 0, rounds1 = 0;      // rounds: hand-overs of accumulator 0 / 1 so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
             const int nsl = t.n_pad >> 4;
@@ -493,12 +504,13 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < 16; ++c) sum[i][c] = 0.f;
             bool ok = true;
-            for (int kb = 0; kb < KB; ++kb) {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
                 if (!chunk_ends(kb, KB)) continue;
-                const uint32_t buf = kb & 1;
+                const uint32_t buf = it & 1;
                 const uint32_t par = (buf ? rounds1 : rounds0) & 1;
                 if (buf) ++rounds1; else ++rounds0;
-                if (!mbar_wait(smem_u32(&s_acc_full[buf]), par, abort_flag)) { ok = false; break; }
+                // the warp stays converged for the .aligned TMEM instructions, also when a wait is abandoned
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_acc_full[buf]), par, abort_flag))) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int i = 0; i < C::SLICES; ++i) {
@@ -564,7 +576,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         bool ok = total_it > 0 && !*abort_flag;
         auto fetch = [&](uint32_t it) -> bool {
             const int s = it % W_STAGES;
-            if (!mbar_wait(smem_u32(&s_w_full[s]), (it / W_STAGES) & 1, abort_flag)) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_w_full[s]), (it / W_STAGES) & 1, abort_flag))) return false;
             const uint8_t* row = w_ring_ptr + s * W_TILE + r * ROW_BYTES;
 #pragma unroll
             for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
@@ -587,7 +599,10 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 }
             }
             // the MMAs that read this TMEM buffer WBUFS k blocks ago must be done
-            if (!mbar_wait(smem_u32(&s_wb_free[wb]), ((it / WBUFS) & 1) ^ 1, abort_flag)) break;
+            if (it >= (uint32_t)WBUFS) {
+                const uint32_t prev = it - WBUFS;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_wb_free[prev % PW]), (prev / PW) & 1, abort_flag))) break;
+            }
             tc_fence_after();
             const uint32_t dst = tlane + wb * WBUF_STRIDE;
             tmem_st32(dst, hi);
@@ -595,7 +610,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             if (it + 1 < total_it) ok = fetch(it + 1);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(smem_u32(&s_wb_ready[wb]));
+            mbar_arrive(smem_u32(&s_wb_ready[it % PW]));
         }
     }
 
