@@ -35,9 +35,9 @@
 // truncation, not round-to-nearest: measured on B200, one accumulator carried
 // over K = 1024..2048 drifts by about 1.5e-5 relative, and the drift grows
 // linearly with the number of MMAs.  So a TMEM accumulator only ever holds the
-// sum of one chunk of 8 k blocks (96 MMAs); the accumulate warps add each
-// finished chunk into a running sum in registers with round-to-nearest adds
-// and clear the columns again, so every MMA accumulates (none overwrites).
+// sum of one chunk of 8 k blocks (96 MMAs, the first one overwriting); the
+// accumulate warps add each finished chunk into a running sum in registers
+// with round-to-nearest adds.
 //
 // Two MMA issuers, one accumulator each.  A tf32 MMA of this shape (128 x 144 x 8) runs for only
 // ~72 cycles and the tensor pipe accepts few instructions ahead, so a single issuing thread leaves
@@ -56,8 +56,7 @@
 //                 allocation); a commit per k block frees the token stage and the TMEM weight buffer,
 //                 a commit per chunk hands the issuer's accumulator to the accumulate warps
 //   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and
-//                 every other 16-column slice per warp), add into registers, clear the
-//                 columns; after the last chunk gelu*dot + TF32 split (lane pairs exchange a
+//                 every other 16-column slice per warp), add into registers; after the last chunk gelu*dot + TF32 split (lane pairs exchange a
 //                 and b by shuffle) or residual add, stores contiguous over the weight-row index
 //   warps 10..13  transform: weight tile shared memory -> registers -> hi/lo -> TMEM
 //   warp 14       TMA producer of the token ring (T_STAGES x two planes)
@@ -168,13 +167,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Clears 16 consecutive TMEM columns of this thread's lane.
-__device__ __forceinline__ void tmem_zero16(uint32_t taddr) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(0u)
-        : "memory");
-}
 // Stores 32 consecutive TMEM columns of this thread's lane.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -234,8 +226,8 @@ struct Cfg {
     static constexpr int A_STAGE = 2 * A_TILE;
     static constexpr int SMEM = W_STAGES * W_TILE + T_STAGES * A_STAGE + 1024;   // + slack for 1024-byte alignment
     static constexpr int PA = barrier_period(T_STAGES);             // barriers of the token ring
-    static constexpr int SLICES = NMAX / 32;                        // 16-column slices owned by one epilogue thread
-    static_assert(NMAX % 32 == 0 && NMAX <= ACC_STRIDE, "token chunk");
+    static constexpr int SLICES = (NMAX / 16 + 1) / 2;              // 16-column slices owned by one epilogue thread
+    static_assert(NMAX % 16 == 0 && NMAX <= ACC_STRIDE, "token chunk");
     static_assert(A_TILE % 1024 == 0, "tiles must keep 1024-byte alignment");
 };
 
@@ -307,7 +299,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     __shared__ __align__(8) uint64_t s_wb_ready[PW];        // transform -> MMA: TMEM weight buffer filled
     __shared__ __align__(8) uint64_t s_wb_free[PW];         // MMA -> transform: TMEM weight buffer consumed
     __shared__ __align__(8) uint64_t s_acc_full[2];         // MMA issuer i -> accumulate warps: chunk of accumulator i done
-    __shared__ __align__(8) uint64_t s_acc_empty[2];        // accumulate warps -> MMA: drained and cleared
+    __shared__ __align__(8) uint64_t s_acc_empty[2];        // accumulate warps -> MMA issuer i: chunk read out
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_prefix[MAX_EXPERTS + 1];
@@ -442,15 +434,16 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             bool ok = true, entered = false;   // entered: the accumulator has been taken over for the current chunk
             for (int kb = 0; kb < KB; ++kb, ++it) {
                 if ((it & 1u) != mine) continue;
-                if (!entered) {  // the accumulator must have been drained and cleared
+                if (!entered) {  // the accumulator's previous chunk must have been read out
                     if (!mbar_wait(acc_empty, rounds & 1, abort_flag)) { ok = false; break; }
-                    entered = true;
                 }
                 const int s = it % T_STAGES;
                 const uint32_t wb = it % WBUFS;
                 if (!mbar_wait(smem_u32(&s_a_full[it % C::PA]), (it / C::PA) & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(smem_u32(&s_wb_ready[it % PW]), (it / PW) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
+                const bool first = !entered;       // first k block of a chunk: its first MMA overwrites the accumulator
+                entered = true;
                 if (leader) {
                     const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
                     const uint32_t w_hi = tmem_base + WBUF_COL + wb * WBUF_STRIDE, w_lo = w_hi + BK;
@@ -459,7 +452,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     for (int ks = 0; ks < BK / 8; ++ks) {
                         // 8 TF32 = 32 bytes along K inside the swizzled row = 2 units of the descriptor address
                         const uint64_t b_hi = d_a_hi + 2 * ks, b_lo = d_a_lo + 2 * ks;
-                        umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, 1u);   // small terms first
+                        umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, (first && ks == 0) ? 0u : 1u);   // small terms first
                         umma_tf32_ts(d, w_hi + ks * 8, b_lo, idesc, 1u);
                         umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
                     }
@@ -477,21 +470,14 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     } else if (warp < 2 + EPI_WARPS) {
         // ================= accumulate + epilogue (warps 2..9) =================
-        // Each chunk is accumulated in TMEM from a cleared accumulator and added here, with
-        // round-to-nearest adds, to a running sum in registers; the columns are cleared again
-        // before the accumulator goes back to its MMA issuer.  The chunks of the two accumulators
-        // are taken in the fixed order of their last k block.
+        // Each chunk is accumulated in TMEM (its first MMA overwrites the accumulator) and added
+        // here, with round-to-nearest adds, to a running sum in registers; then the accumulator
+        // goes back to its MMA issuer.  The chunks of the two accumulators are taken in the fixed
+        // order of their last k block.
         const int q = warp & 3;                 // TMEM lane quarter this warp may access
         const int half = (warp - 2) >> 2;       // even or odd 16-column slices
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
-        // first hand-over: both accumulators cleared
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-#pragma unroll
-            for (int i = 0; i < C::SLICES; ++i) tmem_zero16(tlane + b * ACC_STRIDE + (2 * i + half) * 16);
-        }
-        tmem_st_wait();
-        tc_fence_before();
+        // first hand-over: both accumulators are free
         mbar_arrive(smem_u32(&s_acc_empty[0]));
         mbar_arrive(smem_u32(&s_acc_empty[1]));
         uint32_t it = 0, rounds0 = 0, rounds1 = 0;      // rounds: hand-overs of accumulator 0 / 1 so far
@@ -519,12 +505,10 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         uint32_t r[16];
                         tmem_ld16(tlane + buf * ACC_STRIDE + sl * 16, r);
                         tmem_ld_wait();
-                        tmem_zero16(tlane + buf * ACC_STRIDE + sl * 16);
 #pragma unroll
                         for (int c = 0; c < 16; ++c) sum[i][c] = __fadd_rn(sum[i][c], __uint_as_float(r[c]));
                     }
                 }
-                tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(smem_u32(&s_acc_empty[buf]));
             }
@@ -583,10 +567,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
             return true;
         };
-        if (ok) ok = fetch(0);
-        for (uint32_t it = 0; ok && it < total_it; ++it) {
-            const uint32_t wb = it % WBUFS;
-            uint32_t hi[32], lo[32];
+        uint32_t hi[32], lo[32];
+        auto split = [&]() {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const float x[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
@@ -598,16 +580,24 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     lo[4 * c + j] = __float_as_uint(l);
                 }
             }
+        };
+        if (ok) ok = fetch(0);
+        if (ok) split();
+        for (uint32_t it = 0; ok && it < total_it; ++it) {
             // the MMAs that read this TMEM buffer WBUFS k blocks ago must be done
             if (it >= (uint32_t)WBUFS) {
                 const uint32_t prev = it - WBUFS;
                 if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_wb_free[prev % PW]), (prev / PW) & 1, abort_flag))) break;
             }
             tc_fence_after();
-            const uint32_t dst = tlane + wb * WBUF_STRIDE;
+            const uint32_t dst = tlane + (it % WBUFS) * WBUF_STRIDE;
             tmem_st32(dst, hi);
             tmem_st32(dst + BK, lo);
-            if (it + 1 < total_it) ok = fetch(it + 1);
+            // while the stores are in flight: read and split the next tile
+            if (it + 1 < total_it) {
+                ok = fetch(it + 1);
+                if (ok) split();
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(smem_u32(&s_wb_ready[it % PW]));
@@ -745,8 +735,7 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     } while (0)
     switch (variant) {
         case 1: INFMOE_LAUNCH_PAIR(160, 3, 4); break;
-        case 2: INFMOE_LAUNCH_PAIR(160, 6, 3); break;
-        case 3: INFMOE_LAUNCH_PAIR(128, 3, 5); break;
+        case 2: INFMOE_LAUNCH_PAIR(144, 4, 4); break;
         default: INFMOE_LAUNCH_PAIR(160, 5, 3); break;
     }
 #undef INFMOE_LAUNCH_PAIR
