@@ -39,7 +39,7 @@ from infmoe_b200 import synth  # noqa: E402
 
 # DRAM bytes the wi_0/wi_1 GEMM moves per weight element (ncu capture summarised under profiles/; 4 = each raw
 # FP32 weight crosses HBM once)
-TRAFFIC_BYTES_PER_WEIGHT = 4.2
+TRAFFIC_BYTES_PER_WEIGHT = 4.28
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
