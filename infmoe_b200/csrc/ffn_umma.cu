@@ -39,16 +39,16 @@
 // accumulate warps add each finished chunk into a running sum in registers
 // with round-to-nearest adds.
 //
-// Two MMA issuers, one accumulator each.  A tf32 MMA of this shape (128 x 144 x 8) runs for only
-// ~72 cycles and the tensor pipe accepts few instructions ahead, so a single issuing thread leaves
-// the pipe idle whenever it waits on a barrier or commits (measured: ~900 of ~1870 cycles per
-// k block).  Two warps therefore issue alternate k blocks: the barrier waits of one overlap the
-// issue of the other.  MMAs issued by different threads are not ordered against one another (two
-// issuers adding into ONE accumulator lost updates once the pipe was saturated), so each issuer owns
-// a TMEM accumulator: the MMAs into one accumulator all come from one thread, in k order, and the
-// result does not depend on timing.  The chunk boundaries of the two accumulators are half a chunk
-// apart, so while one accumulator is drained the other issuer keeps the pipe busy; the same
-// overlap hides the epilogue behind the next tile's MMAs.
+// Two MMA issuers, one accumulator each.  The 12 MMAs of a k block, the barrier waits before them
+// and the commits after them do not fit into the time the tensor pipe needs for the block when a
+// single thread does all of it (measured: ~900 of ~1870 cycles per k block idle).  Two warps
+// therefore issue alternate k blocks: the barrier waits of one overlap the issue of the other.
+// MMAs issued by different threads into one accumulator complete correctly but in no defined order
+// (checked on B200 with integer-valued operands: no update is lost), and the truncating accumulate
+// is not associative, so each issuer owns a TMEM accumulator: the MMAs into one accumulator all
+// come from one thread, in k order, and the result does not depend on timing.  The chunk boundaries
+// of the two accumulators are half a chunk apart, so while one accumulator is read out the other
+// issuer keeps the pipe busy; the same overlap hides the epilogue behind the next tile's MMAs.
 //
 // Pipeline per CTA (persistent, one CTA per SM, 16 warps):
 //   warp 0        TMA producer of the weight ring (W_STAGES x 16 KB, raw FP32)
