@@ -112,6 +112,24 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     lo = __fsub_rn(x, hi);
 }
 
+// Two FP32 values rounded to BF16 (round to nearest even) in one 32-bit word: `even` in the lower half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float even, float odd) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(odd), "f"(even));
+    return r;
+}
+
+// Token operand of the tensor-core GEMM, per value x: hi = x rounded to TF32 (FP32 plane `hi`), and the BF16
+// roundings of hi and of lo = x - hi in a packed plane.  The packed plane has one 128-byte group per 32 values
+// of a row: 32 x bf16(hi) followed by 32 x bf16(lo); rows are padded with zeros to a multiple of 32 values.
+__host__ __device__ __forceinline__ size_t pack_pitch(int K) { return (size_t)((K + 31) / 32) * 64; }   // in BF16 elements
+// Stores the packed entries of four consecutive values k0..k0+3 (k0 a multiple of 4) of one row.
+__device__ __forceinline__ void store_pack4(uint16_t* __restrict__ pack_row, int k0, const float hi[4], const float lo[4]) {
+    uint16_t* g = pack_row + (size_t)(k0 >> 5) * 64 + (k0 & 31);
+    *reinterpret_cast<uint2*>(g) = make_uint2(pack_bf16x2(hi[0], hi[1]), pack_bf16x2(hi[2], hi[3]));
+    *reinterpret_cast<uint2*>(g + 32) = make_uint2(pack_bf16x2(lo[0], lo[1]), pack_bf16x2(lo[2], lo[3]));
+}
+
 // gelu(a) * b in the reference's evaluation order (plugin/cuda/ops/gelu.cu:8-15).
 __device__ __forceinline__ float gelu_dot(float a, float b) {
     const float cdf = 0.5f * (1.0f + tanhf(a * (0.035677408136300125f * a * a + 0.7978845608028654f)));

@@ -151,6 +151,16 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with BF16 operands (K = 16 per instruction): A is 128 lanes x 8 columns holding two BF16 each.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Arrives on the mbarrier once all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -195,9 +205,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     return d;
 }
 
-// Instruction descriptor: FP32 accumulate, TF32 x TF32, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UMMA_M >> 4) << 24);
+// Instruction descriptors: FP32 accumulate, both operands K-major, M = 128, N = n; operand format 2 = TF32
+// (kind::tf32), 1 = BF16 (kind::f16).
+__device__ __forceinline__ uint32_t make_idesc(int n, uint32_t fmt) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UMMA_M >> 4) << 24);
 }
 
 enum { EPI_GELU_PAIR = 0, EPI_RESIDUAL = 1 };
@@ -404,14 +415,15 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     }
                     const uint32_t bar = smem_u32(&s_a_full[it % C::PA]);
                     mbar_expect_tx(bar, a_bytes);
-                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
+                    // head plane: 32 floats of the row; packed plane: the row's 64 BF16 of this k block
+                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_pk = a_hi + C::A_TILE;
                     if (big) {
                         tma_load_2d(a_hi, &map_b_hi, bar, kb * BK, t.row0);
-                        tma_load_2d(a_lo, &map_b_lo, bar, kb * BK, t.row0);
+                        tma_load_2d(a_pk, &map_b_lo, bar, kb * 2 * BK, t.row0);
                     } else {
                         for (int b = 0; b < nbox; ++b) {
                             tma_load_2d(a_hi + b * 32 * ROW_BYTES, &map_a_hi, bar, kb * BK, t.row0 + b * 32);
-                            tma_load_2d(a_lo + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * BK, t.row0 + b * 32);
+                            tma_load_2d(a_pk + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * 2 * BK, t.row0 + b * 32);
                         }
                     }
                 }
@@ -430,7 +442,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         uint32_t it = 0, rounds = 0;   // rounds: hand-overs of this issuer's accumulator so far
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
             const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
-            const uint32_t idesc = make_idesc(t.n_pad);
+            const uint32_t idesc_tf32 = make_idesc(t.n_pad, 2u), idesc_bf16 = make_idesc(t.n_pad, 1u);
             bool ok = true, entered = false;   // entered: the accumulator has been taken over for the current chunk
             for (int kb = 0; kb < KB; ++kb, ++it) {
                 if ((it & 1u) != mine) continue;
@@ -445,17 +457,20 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 const bool first = !entered;       // first k block of a chunk: its first MMA overwrites the accumulator
                 entered = true;
                 if (leader) {
-                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_lo = a_hi + C::A_TILE;
-                    const uint32_t w_hi = tmem_base + WBUF_COL + wb * WBUF_STRIDE, w_lo = w_hi + BK;
-                    const uint64_t d_a_hi = make_smem_desc(a_hi), d_a_lo = make_smem_desc(a_lo);
+                    const uint32_t a_hi = a_ring + s * C::A_STAGE, a_pk = a_hi + C::A_TILE;
+                    const uint32_t w_hi = tmem_base + WBUF_COL + wb * WBUF_STRIDE, w_pk = w_hi + BK;
+                    const uint64_t d_a_hi = make_smem_desc(a_hi), d_a_pk = make_smem_desc(a_pk);
+                    // corrections first (small terms), in BF16 with K = 16 per instruction: tail(w) x head(x) and
+                    // head(w) x tail(x).  In the packed token row bf16(head) is bytes 0..63, bf16(tail) bytes 64..127;
+                    // 32 bytes along K = 2 units of the descriptor address.
 #pragma unroll
-                    for (int ks = 0; ks < BK / 8; ++ks) {
-                        // 8 TF32 = 32 bytes along K inside the swizzled row = 2 units of the descriptor address
-                        const uint64_t b_hi = d_a_hi + 2 * ks, b_lo = d_a_lo + 2 * ks;
-                        umma_tf32_ts(d, w_lo + ks * 8, b_hi, idesc, (first && ks == 0) ? 0u : 1u);   // small terms first
-                        umma_tf32_ts(d, w_hi + ks * 8, b_lo, idesc, 1u);
-                        umma_tf32_ts(d, w_hi + ks * 8, b_hi, idesc, 1u);
+                    for (int j = 0; j < BK / 16; ++j) {
+                        umma_bf16_ts(d, w_pk + 8 * j, d_a_pk + 2 * j, idesc_bf16, (first && j == 0) ? 0u : 1u);
+                        umma_bf16_ts(d, w_pk + 16 + 8 * j, d_a_pk + 4 + 2 * j, idesc_bf16, 1u);
                     }
+                    // head(w) x head(x) in TF32, K = 8 per instruction
+#pragma unroll
+                    for (int ks = 0; ks < BK / 8; ++ks) umma_tf32_ts(d, w_hi + ks * 8, d_a_hi + 2 * ks, idesc_tf32, 1u);
                     // token stage and TMEM weight buffer are free once these MMAs have completed
                     umma_commit(smem_u32(&s_a_empty[it % C::PA]));
                     umma_commit(smem_u32(&s_wb_free[it % PW]));
@@ -529,9 +544,19 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         const float a = (lane & 1) ? other : v, b = (lane & 1) ? v : other;
                         float hi, lo;
                         split_tf32(gelu_dot(a, b), hi, lo);
-                        if (col < t.n_tok && m_ok) {
-                            const size_t o = (size_t)(t.row0 + col) * (size_t)(args.M_total >> 1) + (size_t)(m >> 1);
-                            if (lane & 1) args.out_lo[o] = lo; else args.out_hi[o] = hi;
+                        // even lane: head plane; odd lane: packed plane, which is zero padded to whole groups of
+                        // 32 (weight rows past the matrix are zero in the tiled layout, so those values are 0)
+                        const int F = args.M_total >> 1, f = m >> 1;
+                        if (col < t.n_tok) {
+                            if (!(lane & 1)) {
+                                if (m_ok) args.out_hi[(size_t)(t.row0 + col) * (size_t)F + (size_t)f] = hi;
+                            } else if (f < ((F + 31) & ~31)) {
+                                uint16_t* g = reinterpret_cast<uint16_t*>(args.out_lo) +
+                                              (size_t)(t.row0 + col) * pack_pitch(F) + (size_t)(f >> 5) * 64 + (f & 31);
+                                const uint32_t hl = pack_bf16x2(hi, lo);
+                                g[0] = (uint16_t)(hl & 0xffffu);
+                                g[32] = (uint16_t)(hl >> 16);
+                            }
                         }
                     } else {
                         if (col < t.n_tok && m_ok) {
@@ -567,18 +592,22 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
             return true;
         };
-        uint32_t hi[32], lo[32];
+        // hi: the 32 values rounded to TF32; pk: 16 words of bf16(tail) pairs, then 16 words of bf16(head) pairs
+        uint32_t hi[32], pk[32];
         auto split = [&]() {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const float x[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+                float h[4], l[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    float h, l;
-                    split_tf32(x[j], h, l);
-                    hi[4 * c + j] = __float_as_uint(h);
-                    lo[4 * c + j] = __float_as_uint(l);
+                    split_tf32(x[j], h[j], l[j]);
+                    hi[4 * c + j] = __float_as_uint(h[j]);
                 }
+                pk[2 * c] = pack_bf16x2(l[0], l[1]);
+                pk[2 * c + 1] = pack_bf16x2(l[2], l[3]);
+                pk[16 + 2 * c] = pack_bf16x2(h[0], h[1]);
+                pk[16 + 2 * c + 1] = pack_bf16x2(h[2], h[3]);
             }
         };
         if (ok) ok = fetch(0);
@@ -592,7 +621,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             tc_fence_after();
             const uint32_t dst = tlane + (it % WBUFS) * WBUF_STRIDE;
             tmem_st32(dst, hi);
-            tmem_st32(dst + BK, lo);
+            tmem_st32(dst + BK, pk);
             // while the stores are in flight: read and split the next tile
             if (it + 1 < total_it) {
                 ok = fetch(it + 1);
@@ -640,18 +669,22 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// map over a plane [slots][rows][K] (K contiguous); box = BK x box_rows (x 1), 128-byte swizzle
-int make_map(CUtensorMap* map, const float* base, uint64_t K, uint64_t rows, uint64_t slots, int box_rows, int rank) {
+// map over an FP32 plane [slots][rows][K] (K contiguous), or over the packed BF16 plane [rows][K] with K counted
+// in BF16 elements; box = 128 bytes x box_rows (x 1), 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, uint64_t K, uint64_t rows, uint64_t slots, int box_rows, int rank,
+             bool bf16 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
         return INFMOE_ERR_CUDA;
     }
     cuuint64_t dims[3] = {K, rows, slots};
-    cuuint64_t strides[2] = {K * 4, K * rows * 4};
-    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    const uint64_t esz = bf16 ? 2 : 4;
+    cuuint64_t strides[2] = {K * esz, K * rows * esz};
+    cuuint32_t box[3] = {(cuuint32_t)(ROW_BYTES / esz), (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, (void*)base, dims, strides, box,
+    const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                          (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box,
                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -672,9 +705,9 @@ int launch_one(const GemmArgs& args, long long T, int slots, const float* w, con
     const uint64_t w_rows = (uint64_t)slots * ((args.M_total + UMMA_M - 1) / UMMA_M) * ((args.K + BK - 1) / BK) * UMMA_M;
     INFMOE_TRY(make_map(&m[0], w, BK, w_rows, 1, UMMA_M, 2));
     INFMOE_TRY(make_map(&m[1], a_hi, args.K, (uint64_t)T, 1, 32, 2));
-    INFMOE_TRY(make_map(&m[2], a_lo, args.K, (uint64_t)T, 1, 32, 2));
+    INFMOE_TRY(make_map(&m[2], a_lo, pack_pitch(args.K), (uint64_t)T, 1, 32, 2, true));
     INFMOE_TRY(make_map(&m[3], a_hi, args.K, (uint64_t)T, 1, NMAX, 2));
-    INFMOE_TRY(make_map(&m[4], a_lo, args.K, (uint64_t)T, 1, NMAX, 2));
+    INFMOE_TRY(make_map(&m[4], a_lo, pack_pitch(args.K), (uint64_t)T, 1, NMAX, 2, true));
     auto kern = ffn_umma_kernel<EPI, NMAX, W_STAGES, T_STAGES>;
     INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], m[4], args);

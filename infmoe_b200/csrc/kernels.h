@@ -16,7 +16,7 @@ int launch_dispatch(const int* gate, long long T, int E, int* pos, int* count, i
 int launch_scatter(long long T, int D, const float* X, const float* coeff, const int* pos, float* routed,
                    float* rcoeff, cudaStream_t stream);
 int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
-                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo,
+                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo, bool pack,
                             cudaStream_t stream);
 int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream);
 int launch_mix_gather(long long T, int D, const int* pos, const float* routed, const float* post,
@@ -27,11 +27,16 @@ int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_
 // Tile-contiguous weight layout (see rows.cu); src1 != NULL interleaves the rows of two matrices.
 int launch_retile(const float* src0, const float* src1, int M, int K, float* dst, cudaStream_t stream);
 inline size_t tiled_elems(int M, int K) { return (size_t)((M + 127) / 128) * 128 * (size_t)((K + 31) / 32) * 32; }
-int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
+int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo, bool pack,
                     cudaStream_t stream);
+// Bytes of the second activation plane of a [rows][K] operand: FP32 tail plane (CUDA-core GEMM) or packed BF16
+// plane with rows padded to whole groups of 32 values (tensor-core GEMM); the larger of the two.
+inline size_t second_plane_bytes(long long rows, int K) { return (size_t)rows * (size_t)((K + 31) / 32) * 128; }
 
 // Expert weights live in two raw FP32 planes in tile-contiguous layout (128 x 32 tiles, see launch_retile):
-// w01 [slots] x tiled(2F x D) (row 2f = wi_0[f], row 2f+1 = wi_1[f]) and wo [slots] x tiled(D x F).  Activations travel as TF32 head/tail planes (hi = value rounded to TF32, lo = value - hi).
+// w01 [slots] x tiled(2F x D) (row 2f = wi_0[f], row 2f+1 = wi_1[f]) and wo [slots] x tiled(D x F).  
+// Activations travel as two planes: hi = value rounded to TF32 (FP32 [rows][K]) and either lo = value - hi
+// (FP32 [rows][K], CUDA-core GEMM) or the packed BF16 plane of common.cuh (tensor-core GEMM).
 int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int* offset, const int* slot_of_expert,
                     const float* h_hi, const float* h_lo, const float* w01, const float* wo, const float* routed,
                     float* g_hi, float* g_lo, float* post, cudaStream_t stream);

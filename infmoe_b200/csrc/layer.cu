@@ -181,9 +181,9 @@ WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     w.routed = take(4 * t * D);
     w.post = take(4 * t * D);
     w.h_hi = take(4 * t * D);
-    w.h_lo = take(4 * t * D);
+    w.h_lo = take(second_plane_bytes((long long)t, L->D));
     w.g_hi = take(4 * t * F);
-    w.g_lo = take(4 * t * F);
+    w.g_lo = take(second_plane_bytes((long long)t, L->F));
     w.slots = take(streamed && !L->identity
                        ? 4 * (size_t)L->mc * (tiled_elems(2 * L->F, L->D) + tiled_elems(L->D, L->F) + 3 * D * F)
                        : 0);
@@ -686,8 +686,9 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
         INFMOE_CUDA_TRY(cudaMemcpyAsync(post, routed, sizeof(float) * (size_t)T * L->D, cudaMemcpyDeviceToDevice, stream));
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
+        const bool pack = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);   // the GEMM run_ffn picks
         INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate_in, s->d_ln, routed, rscore, h_hi, h_lo,
-                                           stream));
+                                           pack, stream));
         INFMOE_TRY(prof_mark(L, 3, stream));
         // 4. experts (:360-402)
         if (!streamed) {
@@ -1099,7 +1100,8 @@ int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* byte
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    *bytes = 2 * align_up(4 * r * d) + 2 * align_up(4 * r * f) + align_up(4 * tiled_elems(2 * F, D)) +
+    *bytes = align_up(4 * r * d) + align_up(second_plane_bytes(rows, D)) + align_up(4 * r * f) +
+             align_up(second_plane_bytes(rows, F)) + align_up(4 * tiled_elems(2 * F, D)) +
              align_up(4 * tiled_elems(D, F)) + 2 * ALIGN + ALIGN;
     return INFMOE_OK;
 }
@@ -1126,9 +1128,9 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
         return at;
     };
     float* h_hi = (float*)take(4 * r * d);
-    float* h_lo = (float*)take(4 * r * d);
+    float* h_lo = (float*)take(second_plane_bytes(rows, D));
     float* g_hi = (float*)take(4 * r * f);
-    float* g_lo = (float*)take(4 * r * f);
+    float* g_lo = (float*)take(second_plane_bytes(rows, F));
     float* planes[2];
     planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
     planes[1] = (float*)take(4 * tiled_elems(D, F));
@@ -1137,13 +1139,13 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
     const int h_offset[2] = {0, (int)rows};
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
+    const char* path = getenv("INFMOE_FFN");
+    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
+    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, !simt, stream));
     INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const char* path = getenv("INFMOE_FFN");
-    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
     if (simt)
         INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
                                    y, stream));
@@ -1240,9 +1242,9 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
         return at;
     };
     float* h_hi = (float*)take(4 * r * d);
-    float* h_lo = (float*)take(4 * r * d);
+    float* h_lo = (float*)take(second_plane_bytes(rows, D));
     float* g_hi = (float*)take(4 * r * f);
-    float* g_lo = (float*)take(4 * r * f);
+    float* g_lo = (float*)take(second_plane_bytes(rows, F));
     float* planes[2];
     planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
     planes[1] = (float*)take(4 * tiled_elems(D, F));
@@ -1253,13 +1255,13 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     const int h_offset[2] = {0, (int)rows};
     INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
     INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, stream));
+    const char* path = getenv("INFMOE_FFN");
+    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
+    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, !simt, stream));
     INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
     int dev = 0, sms = 0;
     INFMOE_CUDA_TRY(cudaGetDevice(&dev));
     INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const char* path = getenv("INFMOE_FFN");
-    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
     if (simt)
         INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
                                    y, stream));

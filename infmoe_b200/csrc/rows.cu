@@ -42,8 +42,11 @@ scatter_kernel(long long T, int D, int vec, const float* __restrict__ X, const f
 
 // The layer's fused scatter: one read of X[pos[j],:] produces the routed row,
 // its per-expert LayerNorm h = LN(x; gamma_e) (T5FFLayer.cc:99-103) already
-// split into TF32 head and tail planes for the tensor-core GEMM, and the
-// routed score.  gamma is [E][D]; the expert of row j is gate[pos[j]].
+// split for the grouped GEMM, and the routed score.  gamma is [E][D]; the
+// expert of row j is gate[pos[j]].  PACK = false: TF32 head and FP32 tail
+// planes h_hi / h_lo [T][D] (exact split, CUDA-core GEMM); PACK = true: head
+// plane h_hi and the packed BF16 plane (see store_pack4) in h_lo (tensor-core GEMM).
+template <bool PACK>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X, const float* __restrict__ score,
                         const int* __restrict__ pos, const int* __restrict__ gate,
@@ -58,28 +61,31 @@ scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X
     const float* gamma = gamma_all + (long long)e * D;
     float mean, rstd;
     warp_row_stats(src, D, vec != 0, mean, rstd);
-    for (int base = 4 * lane; base < D; base += 128) {
-        const float4 v = load_row4(src, base, D, vec != 0);
-        const float4 g = load_row4(gamma, base, D, vec != 0);
-        float4 hi, lo;
-        split_tf32(ln_apply(v.x, mean, rstd, g.x), hi.x, lo.x);
-        split_tf32(ln_apply(v.y, mean, rstd, g.y), hi.y, lo.y);
-        split_tf32(ln_apply(v.z, mean, rstd, g.z), hi.z, lo.z);
-        split_tf32(ln_apply(v.w, mean, rstd, g.w), hi.w, lo.w);
-        const long long o = j * D + base;
-        if (vec) {
-            if (routed) *reinterpret_cast<float4*>(routed + o) = v;
-            *reinterpret_cast<float4*>(h_hi + o) = hi;
-            *reinterpret_cast<float4*>(h_lo + o) = lo;
-        } else {
-            const float vv[4] = {v.x, v.y, v.z, v.w}, hh[4] = {hi.x, hi.y, hi.z, hi.w},
-                        ll[4] = {lo.x, lo.y, lo.z, lo.w};
-            for (int k = 0; k < 4 && base + k < D; ++k) {
-                if (routed) routed[o + k] = vv[k];
-                h_hi[o + k] = hh[k];
-                h_lo[o + k] = ll[k];
+    uint16_t* pack_row = PACK ? reinterpret_cast<uint16_t*>(h_lo) + j * (long long)pack_pitch(D) : nullptr;
+    const int k_end = PACK ? ((D + 31) & ~31) : D;   // the packed plane is zero padded to whole groups
+    for (int base = 4 * lane; base < k_end; base += 128) {
+        float hh[4] = {0.f, 0.f, 0.f, 0.f}, ll[4] = {0.f, 0.f, 0.f, 0.f};
+        if (base < D) {
+            const float4 v = load_row4(src, base, D, vec != 0);
+            const float4 g = load_row4(gamma, base, D, vec != 0);
+            const float vv[4] = {v.x, v.y, v.z, v.w}, gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (base + k < D) split_tf32(ln_apply(vv[k], mean, rstd, gg[k]), hh[k], ll[k]);
+            const long long o = j * D + base;
+            if (vec) {
+                if (routed) *reinterpret_cast<float4*>(routed + o) = v;
+                *reinterpret_cast<float4*>(h_hi + o) = make_float4(hh[0], hh[1], hh[2], hh[3]);
+                if (!PACK) *reinterpret_cast<float4*>(h_lo + o) = make_float4(ll[0], ll[1], ll[2], ll[3]);
+            } else {
+                for (int k = 0; k < 4 && base + k < D; ++k) {
+                    if (routed) routed[o + k] = vv[k];
+                    h_hi[o + k] = hh[k];
+                    if (!PACK) h_lo[o + k] = ll[k];
+                }
             }
         }
+        if (PACK) store_pack4(pack_row, base, hh, ll);
     }
     if (lane == 0 && rscore && score) rscore[j] = score[p];
 }
@@ -145,7 +151,8 @@ layernorm_kernel(long long n, int D, int vec, const float* __restrict__ in, cons
     }
 }
 
-// h = LN(x; gamma) written as TF32 head / tail planes (rows already in place).
+// h = LN(x; gamma) split for the grouped GEMM (rows already in place); planes as in scatter_ln_split_kernel.
+template <bool PACK>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 ln_split_kernel(long long n, int D, int vec, const float* __restrict__ in, const float* __restrict__ gamma,
                 float* __restrict__ h_hi, float* __restrict__ h_lo) {
@@ -155,12 +162,21 @@ ln_split_kernel(long long n, int D, int vec, const float* __restrict__ in, const
     const float* src = in + j * D;
     float mean, rstd;
     warp_row_stats(src, D, vec != 0, mean, rstd);
-    for (int base = 4 * lane; base < D; base += 128) {
-        const float4 v = load_row4(src, base, D, vec != 0);
-        const float4 g = load_row4(gamma, base, D, vec != 0);
-        const float r[4] = {ln_apply(v.x, mean, rstd, g.x), ln_apply(v.y, mean, rstd, g.y),
-                            ln_apply(v.z, mean, rstd, g.z), ln_apply(v.w, mean, rstd, g.w)};
-        for (int k = 0; k < 4 && base + k < D; ++k) split_tf32(r[k], h_hi[j * D + base + k], h_lo[j * D + base + k]);
+    uint16_t* pack_row = PACK ? reinterpret_cast<uint16_t*>(h_lo) + j * (long long)pack_pitch(D) : nullptr;
+    const int k_end = PACK ? ((D + 31) & ~31) : D;
+    for (int base = 4 * lane; base < k_end; base += 128) {
+        float hh[4] = {0.f, 0.f, 0.f, 0.f}, ll[4] = {0.f, 0.f, 0.f, 0.f};
+        if (base < D) {
+            const float4 v = load_row4(src, base, D, vec != 0);
+            const float4 g = load_row4(gamma, base, D, vec != 0);
+            const float vv[4] = {v.x, v.y, v.z, v.w}, gg[4] = {g.x, g.y, g.z, g.w};
+            for (int k = 0; k < 4 && base + k < D; ++k) {
+                split_tf32(ln_apply(vv[k], mean, rstd, gg[k]), hh[k], ll[k]);
+                h_hi[j * D + base + k] = hh[k];
+                if (!PACK) h_lo[j * D + base + k] = ll[k];
+            }
+        }
+        if (PACK) store_pack4(pack_row, base, hh, ll);
     }
 }
 
@@ -230,13 +246,17 @@ int launch_scatter(long long T, int D, const float* X, const float* coeff, const
 }
 
 int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
-                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo,
+                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo, bool pack,
                             cudaStream_t stream) {
     if (T == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(X) && aligned16(routed) && aligned16(h_hi) && aligned16(h_lo) &&
                     aligned16(gamma_all);
-    scatter_ln_split_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate, gamma_all,
-                                                                        routed, rscore, h_hi, h_lo);
+    if (pack)
+        scatter_ln_split_kernel<true><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate,
+                                                                                  gamma_all, routed, rscore, h_hi, h_lo);
+    else
+        scatter_ln_split_kernel<false><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate,
+                                                                                   gamma_all, routed, rscore, h_hi, h_lo);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -282,11 +302,14 @@ int launch_layernorm(float* out, const float* in, long long n, int D, const floa
     return INFMOE_OK;
 }
 
-int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo,
+int launch_ln_split(long long n, int D, const float* in, const float* gamma, float* h_hi, float* h_lo, bool pack,
                     cudaStream_t stream) {
     if (n == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(in) && aligned16(gamma);
-    ln_split_kernel<<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, h_hi, h_lo);
+    if (pack)
+        ln_split_kernel<true><<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, h_hi, h_lo);
+    else
+        ln_split_kernel<false><<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, gamma, h_hi, h_lo);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
