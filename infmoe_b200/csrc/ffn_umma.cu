@@ -1,6 +1,6 @@
-// Grouped expert FFN on the Blackwell tensor cores (sm_100a): tcgen05.mma
-// kind::tf32 with TMEM accumulators, operands staged by TMA, 3xTF32 error
-// compensation so the products keep FP32 accuracy.
+// Grouped expert FFN on the Blackwell tensor cores (sm_100a): tcgen05.mma with
+// TMEM accumulators and a TMEM A operand, operands staged by TMA, split-operand
+// error compensation so the products keep FP32 accuracy.
 //
 // Replaces, for all experts at once, the per-expert sequence of
 // T5FFLayer::run (plugin/sublayers/T5FFLayer.cc:112-138):
@@ -18,31 +18,37 @@
 // two 128-token tiles, and a decode step with 1..64 tokens runs N=16..64 MMAs.
 // The accumulator is D^T: TMEM lane = weight row, TMEM column = token.
 //
-// 3xTF32.  x = hi + lo with hi = x rounded to TF32 and lo = x - hi (exact).
-// Per 8-wide k step three MMAs accumulate lo*hi + hi*lo + hi*hi into the same
-// FP32 accumulator; the dropped lo*lo term is below 2^-22 relative.
-//   * Token operand (N side, read from shared memory by the MMA): the producers of
-//     the activations (scatter + LayerNorm, GEMM-1 epilogue) already write the two
-//     planes, which are small and reused by every weight tile.
-//   * Weight operand (M side): the raw FP32 matrix is streamed from HBM exactly
-//     once, from a tile-contiguous copy made at load time (each 128 x 32 tile is 16 KB
-//     of consecutive addresses, and a CTA's tiles follow one another).  Four transform warps read each
-//     tile from shared memory, split it in registers and store head and tail into TMEM (tcgen05.st); the MMA takes
-//     its A operand from TMEM.  Weights therefore cost 4 bytes per element in HBM,
-//     L2 and shared memory, and the MMA reads only the token tile from shared memory.
+// Split operands.  x = hi + lo with hi = x rounded to TF32 and lo = x - hi (exact).
+// w * x = hi(w) hi(x) + lo(w) hi(x) + hi(w) lo(x) + (a term below 2^-22).  The head product runs as
+// kind::tf32 MMAs (K = 8 each).  The two correction products are 2^-11 of the result, so their
+// operands only need 8 significant bits: they run as kind::f16 MMAs on BF16 copies (K = 16 each,
+// twice the work per instruction and per joule).  A k block of 32 therefore costs 4 BF16 + 4 TF32
+// MMAs into the same FP32 accumulator instead of 12 TF32 MMAs; measured on B200 the layer output
+// stays at 2e-6 relative L2 of the FP64 oracle, and the step is no longer held at the power cap
+// (SM clock 1.9 GHz instead of 1.4 GHz under sustained load).
+//   * Token operand (N side, read from shared memory by the MMA): the producers of the activations
+//     (scatter + LayerNorm, GEMM-1 epilogue) write a head plane (FP32 values rounded to TF32) and a
+//     packed BF16 plane (per 32 values: 32 x bf16(head), 32 x bf16(tail)); both are small and reused
+//     by every weight tile.
+//   * Weight operand (M side): the raw FP32 matrix is streamed from HBM exactly once, from a
+//     tile-contiguous copy made at load time (each 128 x 32 tile is 16 KB of consecutive addresses,
+//     and a CTA's tiles follow one another).  Four transform warps read each tile from shared memory,
+//     split it in registers with integer arithmetic and store head, bf16(tail) and bf16(head) into
+//     TMEM (tcgen05.st); the MMAs take their A operand from TMEM.  Weights therefore cost 4 bytes per
+//     element in HBM, L2 and shared memory, and the MMA reads only the token tile from shared memory.
 //
 // Chunked accumulation.  The tensor core adds into its FP32 accumulator with
 // truncation, not round-to-nearest: measured on B200, one accumulator carried
 // over K = 1024..2048 drifts by about 1.5e-5 relative, and the drift grows
 // linearly with the number of MMAs.  So a TMEM accumulator only ever holds the
-// sum of one chunk of 8 k blocks (96 MMAs, the first one overwriting); the
+// sum of one chunk of 8 k blocks (64 MMAs, the first one overwriting); the
 // accumulate warps add each finished chunk into a running sum in registers
 // with round-to-nearest adds.
 //
-// Two MMA issuers, one accumulator each.  The 12 MMAs of a k block, the barrier waits before them
-// and the commits after them do not fit into the time the tensor pipe needs for the block when a
-// single thread does all of it (measured: ~900 of ~1870 cycles per k block idle).  Two warps
-// therefore issue alternate k blocks: the barrier waits of one overlap the issue of the other.
+// Two MMA issuers, one accumulator each.  One thread can keep the tensor pipe full only while it does
+// nothing but issue; the barrier waits before a k block and the commits after it leave the pipe idle
+// (measured with one issuer: ~900 of ~1870 cycles per k block).  Two warps therefore issue alternate
+// k blocks: the barrier waits of one overlap the issue of the other.
 // MMAs issued by different threads into one accumulator complete correctly but in no defined order
 // (checked on B200 with integer-valued operands: no update is lost), and the truncating accumulate
 // is not associative, so each issuer owns a TMEM accumulator: the MMAs into one accumulator all
@@ -55,12 +61,13 @@
 //   warp 1, 15    MMA issuers for even / odd k blocks into accumulator 0 / 1 (warp 1 also owns the TMEM
 //                 allocation); a commit per k block frees the token stage and the TMEM weight buffer,
 //                 a commit per chunk hands the issuer's accumulator to the accumulate warps
-//   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and
-//                 every other 16-column slice per warp), add into registers; after the last chunk gelu*dot + TF32 split (lane pairs exchange a
-//                 and b by shuffle) or residual add, stores contiguous over the weight-row index
-//   warps 10..13  transform: weight tile shared memory -> registers -> hi/lo -> TMEM
+//   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and every other
+//                 16-column slice per warp), add into registers; after the last chunk gelu*dot and its
+//                 split (lane pairs exchange a and b by shuffle) or residual add, stores contiguous
+//                 over the weight-row index
+//   warps 10..13  transform: weight tile shared memory -> registers -> head / packed BF16 -> TMEM
 //   warp 14       TMA producer of the token ring (T_STAGES x two planes)
-// TMEM columns: accumulators at 0 and 160, weight head/tail buffers at 320, 384 and 448.
+// TMEM columns: accumulators at 0 and 160, weight buffers (32 head + 32 packed columns) at 320, 384, 448.
 // Tiles are (expert, 128-row weight block, token chunk); the list is derived in
 // the kernel from offset[E+1], so no host synchronisation is needed.  Every
 // mbarrier wait is bounded: on expiry the CTA raises STATUS_WAIT_TIMEOUT, lets
@@ -592,22 +599,27 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_arrive(smem_u32(&s_w_empty[s]));   // the tile is in registers: its slot can be refilled
             return true;
         };
-        // hi: the 32 values rounded to TF32; pk: 16 words of bf16(tail) pairs, then 16 words of bf16(head) pairs
+        // hi: the 32 values rounded to TF32; pk: 16 words of bf16(tail) pairs, then 16 words of bf16(head) pairs.
+        // Integer arithmetic only (the conversion instructions are several times slower than the ALU here):
+        // head = (bits + 0x1000) & ~0x1fff is cvt.rna.tf32 for every finite value; the BF16 halves keep the upper
+        // 16 bits of head and tail (the head has 11 significant bits, so its BF16 copy drops 3 of them; the
+        // error this adds to a correction product is below 2^-19 of the full product).
         uint32_t hi[32], pk[32];
         auto split = [&]() {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const float x[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-                float h[4], l[4];
+                uint32_t h[4], l[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    split_tf32(x[j], h[j], l[j]);
-                    hi[4 * c + j] = __float_as_uint(h[j]);
+                    h[j] = (__float_as_uint(x[j]) + 0x1000u) & 0xffffe000u;
+                    l[j] = __float_as_uint(__fsub_rn(x[j], __uint_as_float(h[j])));
+                    hi[4 * c + j] = h[j];
                 }
-                pk[2 * c] = pack_bf16x2(l[0], l[1]);
-                pk[2 * c + 1] = pack_bf16x2(l[2], l[3]);
-                pk[16 + 2 * c] = pack_bf16x2(h[0], h[1]);
-                pk[16 + 2 * c + 1] = pack_bf16x2(h[2], h[3]);
+                pk[2 * c] = __byte_perm(l[0], l[1], 0x7632);          // upper halves: l[0] low, l[1] high
+                pk[2 * c + 1] = __byte_perm(l[2], l[3], 0x7632);
+                pk[16 + 2 * c] = __byte_perm(h[0], h[1], 0x7632);
+                pk[16 + 2 * c + 1] = __byte_perm(h[2], h[3], 0x7632);
             }
         };
         if (ok) ok = fetch(0);
