@@ -163,7 +163,7 @@ def workload_config(w, n_gpus):
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-def build_layer(w, device, torch):
+def build_layer(w, device, torch, cache_slots=0):
     from infmoe_b200 import MoELayer
 
     x, cent, ln = synth.gen_inputs(w)
@@ -174,6 +174,8 @@ def build_layer(w, device, torch):
             ws = [t.cpu().numpy() for t in synth.gen_expert_torch(w, e, device)]
             layer.set_expert(e, *ws)
         layer.set_residency(0)
+        if cache_slots:
+            layer.set_expert_cache(cache_slots)
     else:
         for e in range(w.expert_count):
             layer.set_expert(e, *synth.gen_expert_torch(w, e, device))
@@ -232,7 +234,7 @@ def run_single(args, w):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     peaks = _peaks()
-    layer, x, cent, ln = build_layer(w, dev, torch)
+    layer, x, cent, ln = build_layer(w, dev, torch, args.cache_slots)
     T, D, F, E = w.tokens, w.embedding_size, w.hidden_size, w.expert_count
     hx = torch.from_numpy(x).pin_memory()
     hout = torch.empty_like(hx).pin_memory()
@@ -310,8 +312,8 @@ def run_single(args, w):
     line = {
         "metric": METRIC, "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32 (3xTF32 tensor-core products, FP32 accumulate)", "data": "synthetic",
-        "config": workload_config(w, 1),
+        "dtype": "f32 (split-operand tensor-core products: TF32 head + BF16 corrections, FP32 accumulate)", "data": "synthetic",
+        "config": dict(workload_config(w, 1), **({"expert_cache_slots": args.cache_slots} if args.cache_slots else {})),
         "e2e": {"value": T / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(hx.numel() * 4),
                 "d2h_bytes_per_step": int(hout.numel() * 4), "ms_per_step": 1e3 * e2e_s},
         "gpu_launches": int(launches), "stage_ms": stage_ms, "active_experts": active,
@@ -334,6 +336,9 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--seq-len", type=int, default=None, help="override the workload's sequence length (tuning)")
+    ap.add_argument("--cache-slots", type=int, default=0,
+                    help="streamed workloads: experts the layer keeps on the device across calls (0 = none, as the "
+                         "reference)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w, scaling = resolve_workload(args)

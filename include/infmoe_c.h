@@ -89,6 +89,16 @@ INFMOE_API int infmoe_layer_set_expert(infmoe_layer* layer, int32_t expert, cons
  * memory owned by the layer; mode -1: choose 1 when they fit. */
 INFMOE_API int infmoe_layer_set_residency(infmoe_layer* layer, int mode);
 
+/* Expert cache of the streamed mode; no counterpart in the reference, whose max_concurrency slots forget their
+ * expert after every call (plugin/MoELayerPlugin.cc:360-402 copies every used expert on every enqueue) and which
+ * leaves smarter scheduling as a TODO.  slots > 0: the layer keeps that many experts (at least max_concurrency) in
+ * device memory of its own across enqueue calls, replacing the least recently used one on a miss, so a decode
+ * loop that keeps hitting the same experts stops paying for the host->device copies; slots = 0 (default): off.
+ * Device memory: slots x 12 * d_model * d_ff bytes, allocated at the next streamed enqueue. */
+INFMOE_API int infmoe_layer_set_expert_cache(infmoe_layer* layer, int32_t slots);
+/* Expert weight bytes enqueue has copied host -> device for this layer object so far (streamed mode). */
+INFMOE_API int infmoe_layer_weight_h2d_bytes(const infmoe_layer* layer, uint64_t* bytes);
+
 /* MoELayerPlugin::getWorkspaceSize (plugin/MoELayerPlugin.cc:253-273) for token_num = B * S. */
 INFMOE_API int infmoe_layer_workspace_bytes(const infmoe_layer* layer, int64_t token_num, size_t* bytes);
 

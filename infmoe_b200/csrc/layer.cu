@@ -69,6 +69,7 @@ struct ExpertStore {
     float* d_plane[2] = {nullptr, nullptr};
     float* d_staging = nullptr;   // 3*D*F floats: landing area of host weights before they are retiled
     std::vector<char> on_device;
+    std::vector<unsigned> version;   // bumped whenever an expert's host weights are replaced (expert caches compare it)
     bool fortran_warning = false;
 
     size_t matrix_elems() const { return (size_t)D * (size_t)F; }
@@ -135,6 +136,20 @@ struct infmoe_layer {
     void* own_ws = nullptr;
     size_t own_io_bytes = 0, own_ws_bytes = 0;
     cudaStream_t own_stream = nullptr;
+
+    // Optional expert cache of the streamed mode (no counterpart in the reference, whose slots forget their
+    // expert after every call): layer-owned slots that keep their expert across enqueue calls; a missing
+    // expert replaces the least recently used slot.
+    int cache_slots = 0;
+    float* d_cache[2] = {nullptr, nullptr};     // [cache_slots] x tiled plane
+    float* d_cache_staging = nullptr;           // [mc] raw landing areas (3 D F floats each)
+    std::vector<int> cache_expert;              // slot -> expert, -1 = empty
+    std::vector<unsigned> cache_version;        // slot -> version of the expert's weights it holds
+    std::vector<int> cache_slot_of;             // expert -> slot, -1 = not cached
+    std::vector<long long> cache_used;          // slot -> tick of the last use
+    long long cache_tick = 0;
+    std::vector<cudaEvent_t> ev_stage;          // landing area k has been retiled and may be overwritten
+    unsigned long long weight_h2d_bytes = 0;    // expert weight bytes copied host -> device by enqueue so far
 
     long long launches_at_create = 0;
 
@@ -358,6 +373,10 @@ void free_device_state(infmoe_layer* L) {
     for (auto e : L->ev_freed) cudaEventDestroy(e);
     if (L->ev_fork) cudaEventDestroy(L->ev_fork);
     for (auto e : L->prof_events) cudaEventDestroy(e);
+    for (auto e : L->ev_stage) cudaEventDestroy(e);
+    for (float* p : L->d_cache)
+        if (p) cudaFree(p);
+    if (L->d_cache_staging) cudaFree(L->d_cache_staging);
     if (L->own_in) cudaFree(L->own_in);
     if (L->own_out) cudaFree(L->own_out);
     if (L->own_ws) cudaFree(L->own_ws);
@@ -376,6 +395,7 @@ std::shared_ptr<ExpertStore> make_store(int E, int D, int F) {
     s->on_host.assign(E, 0);
     s->on_device.assign(E, 0);
     s->ln_on_device.assign(E, 0);
+    s->version.assign(E, 0);
     return s;
 }
 
@@ -547,6 +567,7 @@ int infmoe_layer_initialize(infmoe_layer* L) {
         s->on_host[e] = 1;
         s->on_device[e] = 0;
         s->ln_on_device[e] = 0;
+        ++s->version[e];
     }
     L->initialized = true;
     return INFMOE_OK;
@@ -579,6 +600,7 @@ int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const
         memcpy(s->h_wi0[e], wi0, sizeof(float) * n);
         memcpy(s->h_wi1[e], wi1, sizeof(float) * n);
         memcpy(s->h_wo[e], wo, sizeof(float) * n);
+        ++s->version[e];
         s->on_host[e] = 1;
         s->on_device[e] = 0;
         s->ln_on_device[e] = 0;
@@ -596,6 +618,113 @@ int infmoe_layer_set_residency(infmoe_layer* L, int mode) {
     L->residency_resolved = false;
     return INFMOE_OK;
 }
+
+int infmoe_layer_set_expert_cache(infmoe_layer* L, int32_t slots) {
+    if (!L || slots < 0) {
+        set_error("layer_set_expert_cache: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (L->d_cache[0]) {   // resizing drops what is cached; the slots may still be read by work in flight
+        INFMOE_CUDA_TRY(cudaDeviceSynchronize());
+        for (float*& p : L->d_cache) {
+            cudaFree(p);
+            p = nullptr;
+        }
+        cudaFree(L->d_cache_staging);
+        L->d_cache_staging = nullptr;
+    }
+    L->cache_slots = slots == 0 ? 0 : std::max(slots, L->mc);
+    L->cache_expert.clear();
+    return INFMOE_OK;
+}
+
+int infmoe_layer_weight_h2d_bytes(const infmoe_layer* L, uint64_t* bytes) {
+    if (!L || !bytes) {
+        set_error("layer_weight_h2d_bytes: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    *bytes = L->weight_h2d_bytes;
+    return INFMOE_OK;
+}
+
+namespace {
+
+// Device memory and bookkeeping of the expert cache, created at the first streamed enqueue that uses it.
+int ensure_cache(infmoe_layer* L) {
+    const ExpertStore* s = L->store.get();
+    const int S = L->cache_slots;
+    if (!L->d_cache[0]) {
+        for (int p = 0; p < 2; ++p)
+            INFMOE_CUDA_TRY(cudaMalloc(&L->d_cache[p], sizeof(float) * s->plane_elems(p) * (size_t)S));
+        INFMOE_CUDA_TRY(cudaMalloc(&L->d_cache_staging, sizeof(float) * 3 * s->matrix_elems() * (size_t)L->mc));
+    }
+    if ((int)L->cache_expert.size() != S) {
+        L->cache_expert.assign(S, -1);
+        L->cache_version.assign(S, 0);
+        L->cache_used.assign(S, 0);
+        L->cache_slot_of.assign(L->E, -1);
+    }
+    while ((int)L->ev_ready.size() < S) {
+        cudaEvent_t a, b;
+        INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        L->ev_ready.push_back(a);
+        L->ev_freed.push_back(b);
+    }
+    while ((int)L->ev_stage.size() < L->mc) {
+        cudaEvent_t a;
+        INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        L->ev_stage.push_back(a);
+    }
+    return INFMOE_OK;
+}
+
+struct CachePlan {
+    int slot;
+    bool load;
+};
+
+// Chooses a slot for every active expert, in execution order.  Experts already cached (with current weights)
+// keep their slot; a missing expert takes the least recently used slot that no later expert of this call is
+// waiting for; if every slot is spoken for, the expert needed last gives its slot up and is loaded again later.
+std::vector<CachePlan> plan_cache(infmoe_layer* L, const std::vector<int>& active) {
+    const ExpertStore* s = L->store.get();
+    const int S = L->cache_slots;
+    std::vector<CachePlan> plan(active.size(), CachePlan{-1, true});
+    std::vector<int> reserved_by(S, -1);   // slot -> position in `active` of the cached expert that will use it
+    for (size_t j = 0; j < active.size(); ++j) {
+        const int e = active[j], sl = L->cache_slot_of[e];
+        if (sl >= 0 && L->cache_expert[sl] == e && L->cache_version[sl] == s->version[e]) {
+            plan[j] = CachePlan{sl, false};
+            reserved_by[sl] = (int)j;
+        }
+    }
+    for (size_t j = 0; j < active.size(); ++j) {
+        const int e = active[j];
+        int sl = plan[j].slot;
+        if (plan[j].load) {
+            int victim = -1;
+            for (int v = 0; v < S; ++v)
+                if (reserved_by[v] < 0 && (victim < 0 || L->cache_used[v] < L->cache_used[victim])) victim = v;
+            if (victim < 0) {   // all slots reserved by later hits: take the one needed last
+                for (int v = 0; v < S; ++v)
+                    if (victim < 0 || reserved_by[v] > reserved_by[victim]) victim = v;
+                plan[(size_t)reserved_by[victim]] = CachePlan{-1, true};
+            }
+            sl = victim;
+            if (L->cache_expert[sl] >= 0) L->cache_slot_of[L->cache_expert[sl]] = -1;
+            L->cache_expert[sl] = e;
+            L->cache_version[sl] = s->version[e];
+            L->cache_slot_of[e] = sl;
+            plan[j].slot = sl;
+        }
+        reserved_by[sl] = -1;              // once its GEMMs are queued the slot may be handed on (behind an event)
+        L->cache_used[sl] = ++L->cache_tick;
+    }
+    return plan;
+}
+
+}  // namespace
 
 int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes) {
     if (!L || !bytes || T < 0) {
@@ -715,29 +844,62 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                 return status_to_rc(st);
             }
             std::vector<int> active;
-            for (int e = 0; e < L->E; ++e) {
-                L->h_slot_map[e] = 0;
-                if (L->h_count[e] > 0) {
-                    L->h_slot_map[e] = (int)(active.size() % (size_t)L->mc);
-                    active.push_back(e);
-                }
+            for (int e = 0; e < L->E; ++e)
+                if (L->h_count[e] > 0) active.push_back(e);
+            // slot of every active expert: round robin over the max_concurrency workspace slots (the reference's
+            // scheme, MoELayerPlugin.cc:360-402), or the layer's expert cache when one is configured
+            const bool cached = L->cache_slots > 0;
+            std::vector<CachePlan> plan(active.size());
+            int nslots = L->mc;
+            if (cached) {
+                INFMOE_TRY(ensure_cache(L));
+                plan = plan_cache(L, active);
+                planes[0] = L->d_cache[0];
+                planes[1] = L->d_cache[1];
+                staging = L->d_cache_staging;
+                nslots = L->cache_slots;
+            } else {
+                for (size_t j = 0; j < active.size(); ++j) plan[j] = CachePlan{(int)(j % (size_t)L->mc), true};
             }
+            for (int e = 0; e < L->E; ++e) L->h_slot_map[e] = 0;
+            for (size_t j = 0; j < active.size(); ++j) L->h_slot_map[active[j]] = plan[j].slot;
             INFMOE_CUDA_TRY(cudaMemcpyAsync(slot_map, L->h_slot_map, sizeof(int) * L->E, cudaMemcpyHostToDevice, stream));
-            // copy streams may touch the slots only after everything queued so far on `stream`
+            // copy streams may touch the workspace slots only after everything queued so far on `stream`
             INFMOE_CUDA_TRY(cudaEventRecord(L->ev_fork, stream));
             for (auto cs : L->copy_streams) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_fork, 0));
-            for (size_t j = 0; j < active.size(); ++j) {
-                const int e = active[j];
-                const int slot = (int)(j % (size_t)L->mc);
-                cudaStream_t cs = L->copy_streams[j % L->copy_streams.size()];
-                // the slot is free once the expert that used it (j - mc) has run
-                if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
-                INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e], planes[0] + n0 * slot,
-                                              planes[1] + n1 * slot, true, staging + 3 * n * slot, cs));
-                INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
-                INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
-                INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, L->mc, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
+            size_t loads = 0;
+            bool all_cached = cached && !active.empty();
+            for (const CachePlan& pl : plan) all_cached = all_cached && !pl.load;
+            if (all_cached) {
+                // nothing to copy: one grouped launch over all experts, as in resident mode
+                for (const CachePlan& pl : plan) INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[pl.slot], 0));
+                INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, slot_map, nslots, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
                                    stream));
+                for (const CachePlan& pl : plan) INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[pl.slot], stream));
+            }
+            for (size_t j = 0; j < active.size() && !all_cached; ++j) {
+                const int e = active[j];
+                const int slot = plan[j].slot;
+                if (plan[j].load) {
+                    cudaStream_t cs = L->copy_streams[loads % L->copy_streams.size()];
+                    // the slot is free once the expert that used it last has run (an event that was never
+                    // recorded does not block)
+                    if (cached || j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
+                    // landing area of the raw matrices: one per workspace slot, or max_concurrency of them in
+                    // rotation for the cache, each reusable once its retile kernels are done
+                    const int area = cached ? (int)(loads % (size_t)L->mc) : slot;
+                    if (cached) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_stage[area], 0));
+                    INFMOE_TRY(load_expert_planes(L->D, L->F, s->h_wi0[e], s->h_wi1[e], s->h_wo[e],
+                                                  planes[0] + n0 * slot, planes[1] + n1 * slot, true,
+                                                  staging + 3 * n * area, cs));
+                    if (cached) INFMOE_CUDA_TRY(cudaEventRecord(L->ev_stage[area], cs));
+                    INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
+                    L->weight_h2d_bytes += 3ull * n * sizeof(float);
+                    ++loads;
+                }
+                INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
+                INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, nslots, planes, h_hi, h_lo, routed, g_hi, g_lo,
+                                   post, stream));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[slot], stream));
             }
             INFMOE_TRY(prof_mark(L, 4, stream));   // streamed: copies and both GEMMs are timed together

@@ -112,7 +112,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
             "metric": metric, "value": T_total / (float(ms.item()) * 1e-3), "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms.item()),
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "f32 (3xTF32 tensor-core products, FP32 accumulate)", "data": "synthetic", "config": cfg,
+            "dtype": "f32 (split-operand tensor-core products: TF32 head + BF16 corrections, FP32 accumulate)", "data": "synthetic", "config": cfg,
             "e2e": {"value": T_total / (float(e2e_ms.item()) * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": int(hx.numel() * 4 * world), "d2h_bytes_per_step": int(hout.numel() * 4 * world),
                     "ms_per_step": float(e2e_ms.item())},

@@ -104,6 +104,16 @@ class MoELayer:
     def set_residency(self, mode: int) -> None:
         capi.check(capi.lib().infmoe_layer_set_residency(self._h, int(mode)))
 
+    def set_expert_cache(self, slots: int) -> None:
+        """Streamed mode: keep `slots` experts in device memory across calls (least recently used replaced); 0 = off."""
+        capi.check(capi.lib().infmoe_layer_set_expert_cache(self._h, int(slots)))
+
+    def weight_h2d_bytes(self) -> int:
+        """Expert weight bytes copied host -> device by enqueue so far."""
+        n = ctypes.c_uint64()
+        capi.check(capi.lib().infmoe_layer_weight_h2d_bytes(self._h, ctypes.byref(n)))
+        return int(n.value)
+
     def set_expert(self, expert: int, ln_w, wi0, wi1, wo) -> None:
         """Weights by pointer: numpy arrays (host) or CUDA torch tensors (device)."""
         arrs = [ln_w, wi0, wi1, wo]

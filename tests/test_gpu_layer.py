@@ -114,6 +114,42 @@ def test_streamed_experts_match_resident(torch_cuda, oracle, tmp_path, mc):
     st.terminate()
 
 
+@pytest.mark.parametrize("slots", [2, 3, 6])
+def test_expert_cache_keeps_experts_across_calls(torch_cuda, oracle, tmp_path, slots):
+    """Streamed mode with the layer's expert cache: same bits as resident weights whatever the cache size; with
+    room for every expert the second call copies nothing; replaced weights are not served from the cache."""
+    from infmoe_b200 import synth
+    w = synth.scaled(synth.WORKLOADS["cpm2"], expert_count=6, embedding_size=128, hidden_size=256, batch=1, seq_len=90)
+    res, x, c, ln, experts = _build(w, synth, tmp_path, residency=1)
+    st, *_ = _build(w, synth, tmp_path, residency=0, mc=2)
+    st.set_expert_cache(slots)
+    want = _check(res, w, x, c, ln, experts, oracle, torch_cuda)
+    per_expert = 3 * 4 * w.embedding_size * w.hidden_size
+    got = st.forward_host(x)
+    np.testing.assert_array_equal(got, want)
+    first = st.weight_h2d_bytes()
+    assert first == w.expert_count * per_expert            # every expert is routed to in this workload
+    np.testing.assert_array_equal(st.forward_host(x), want)
+    second = st.weight_h2d_bytes() - first
+    if slots >= w.expert_count:
+        assert second == 0
+    else:
+        assert 0 < second <= w.expert_count * per_expert
+    # a permuted batch routes to the same experts: still nothing to copy when they all fit
+    perm = np.random.default_rng(0).permutation(w.tokens)
+    np.testing.assert_array_equal(st.forward_host(x[perm]), want[perm])
+    if slots >= w.expert_count:
+        assert st.weight_h2d_bytes() == first
+    # new weights for expert 0 (those of expert 1): the cached copy must not be used
+    st.set_expert(0, *experts[1])
+    res.set_expert(0, *experts[1])
+    before = st.weight_h2d_bytes()
+    np.testing.assert_array_equal(st.forward_host(x), res.forward_host(x))
+    assert st.weight_h2d_bytes() - before >= per_expert
+    res.terminate()
+    st.terminate()
+
+
 def test_exact_path_matches_tensor_core_path(torch_cuda, oracle, monkeypatch):
     from infmoe_b200 import synth
     w = synth.scaled(synth.WORKLOADS["base_layer_zipf"], expert_count=8, embedding_size=128, hidden_size=256, batch=2,
