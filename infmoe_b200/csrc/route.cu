@@ -6,8 +6,10 @@
 //   cublasSgemm_v2       plugin/MoELayerPlugin.cc:334-336  (aff = Xs * C^T)
 //   moe_expert_select    plugin/cuda/moe.cu:147-159     (strict '>' scan, first maximum wins)
 //
-// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA of 8 warps owns
-// 32 tokens (TPW = 4 per warp).  Centroids are streamed through shared memory in
+// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA of WARPS warps owns
+// 4 * WARPS tokens (TPW = 4 per warp; WARPS is picked per launch so that the CTAs fill
+// whole waves of the SMs).  The rows of X are read from global memory one 128-float step
+// ahead of their use.  Centroids are streamed through shared memory in
 // tiles of EG experts x KT floats with double-buffered cp.async, so every
 // centroid byte is fetched from L2 once per CTA and every LDS.128 feeds
 // 4 * TPW fused multiply-adds; a warp keeps TPW * EG per-lane partial sums in
@@ -20,8 +22,6 @@ namespace infmoe {
 
 namespace {
 
-constexpr int ROUTE_WARPS = 8;
-constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -32,7 +32,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Fills one shared-memory tile: experts [e0, e0+EG) x floats [k0, k0+KT) of the centroids, zero padded.
-template <int EG, int KT>
+template <int EG, int KT, int ROUTE_THREADS>
 __device__ __forceinline__ void load_centroid_tile(float* __restrict__ tile, const float* __restrict__ C, int E, int D,
                                                    int e0, int k0, bool vec) {
     if (vec) {
@@ -50,11 +50,12 @@ __device__ __forceinline__ void load_centroid_tile(float* __restrict__ tile, con
     }
 }
 
-template <int TPW, int EG, int KT>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+template <int TPW, int EG, int KT, int ROUTE_WARPS>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
              long long T, int D, int E, int vec, int* __restrict__ gate, float* __restrict__ score,
              int* __restrict__ status) {
+    constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
     extern __shared__ __align__(16) float s_tiles[];   // [2][EG][KT]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -86,6 +87,17 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
     }
 
     const int ntiles = (D + KT - 1) / KT;
+    // The row values of step s (floats [128 s, 128 s + 128) of the row; lane l owns 4 of them) are fetched while
+    // step s - 1 is computed; after the last step of an expert group the first step of the next one follows.
+    float4 v_next[TPW], g_next = make_float4(1.f, 1.f, 1.f, 1.f);
+    auto fetch = [&](int base) {
+        if (base < D && warp_live) {
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) v_next[i] = load_row4(rows[i], base, D, vec != 0);
+            if (use_ln) g_next = load_row4(gamma, base, D, vec != 0);
+        }
+    };
+    fetch(4 * lane);
     for (int e0 = 0; e0 < E; e0 += EG) {
         float acc[TPW][EG];
 #pragma unroll
@@ -93,27 +105,31 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
 #pragma unroll
             for (int j = 0; j < EG; ++j) acc[i][j] = 0.f;
 
-        load_centroid_tile<EG, KT>(s_tiles, C, E, D, e0, 0, vec != 0);
+        load_centroid_tile<EG, KT, ROUTE_THREADS>(s_tiles, C, E, D, e0, 0, vec != 0);
         cp_async_commit();
         for (int kt = 0; kt < ntiles; ++kt) {
             const float* tile = s_tiles + (kt & 1) * EG * KT;
             if (kt + 1 < ntiles)
-                load_centroid_tile<EG, KT>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT, vec != 0);
+                load_centroid_tile<EG, KT, ROUTE_THREADS>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT,
+                                                          vec != 0);
             cp_async_commit();
             cp_async_wait<1>();   // tile kt has landed (the group of tile kt+1 may still be in flight)
             __syncthreads();
             if (warp_live) {
-#pragma unroll
+#pragma unroll 1   // one step is 256 FMAs per lane; unrolling further only thrashes the instruction cache
                 for (int it = 0; it < KT / 128; ++it) {
                     const int kl = it * 128 + 4 * lane;       // offset inside the tile
                     const int base = kt * KT + kl;            // offset inside the row
+                    float4 v_cur[TPW];
+#pragma unroll
+                    for (int i = 0; i < TPW; ++i) v_cur[i] = v_next[i];
+                    const float4 g4 = g_next;
+                    fetch(base + 128 < ntiles * KT ? base + 128 : 4 * lane);
                     if (base < D) {
                         float xs[TPW][4];
-                        float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
-                        if (use_ln) g4 = load_row4(gamma, base, D, vec != 0);
 #pragma unroll
                         for (int i = 0; i < TPW; ++i) {
-                            const float4 v = load_row4(rows[i], base, D, vec != 0);
+                            const float4 v = v_cur[i];
                             if (use_ln) {
                                 xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g4.x);
                                 xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g4.y);
@@ -213,11 +229,38 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
     const bool vec = (D % 4 == 0) && (((uintptr_t)X | (uintptr_t)C | (uintptr_t)gamma) % 16 == 0);
     constexpr int TPW = 4, EG = 16, KT = 512;
     constexpr int SMEM = 2 * EG * KT * (int)sizeof(float);
-    const long long tokens_per_cta = (long long)ROUTE_WARPS * TPW;
-    const long long grid = (T + tokens_per_cta - 1) / tokens_per_cta;
-    auto kern = route_kernel<TPW, EG, KT>;
-    INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    kern<<<(unsigned)grid, ROUTE_THREADS, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status);
+    // The kernel is bound by FP32 FMAs, so a CTA's time grows with its warps and the launch takes
+    // waves x warps: pick the warp count (5..8) that wastes the least of the last wave.
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        INFMOE_CUDA_TRY(cudaGetDevice(&dev));
+        INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    int warps = 8;
+    long long best_cost = -1;
+    for (int w = 8; w >= 5; --w) {
+        const long long ctas = (T + (long long)w * TPW - 1) / ((long long)w * TPW);
+        const long long cost = ((ctas + sms - 1) / sms) * w;
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            warps = w;
+        }
+    }
+    const long long grid = (T + (long long)warps * TPW - 1) / ((long long)warps * TPW);
+#define INFMOE_ROUTE_LAUNCH(W)                                                                                     \
+    do {                                                                                                           \
+        auto kern = route_kernel<TPW, EG, KT, W>;                                                                  \
+        INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));            \
+        kern<<<(unsigned)grid, W * 32, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status);     \
+    } while (0)
+    switch (warps) {
+        case 5: INFMOE_ROUTE_LAUNCH(5); break;
+        case 6: INFMOE_ROUTE_LAUNCH(6); break;
+        case 7: INFMOE_ROUTE_LAUNCH(7); break;
+        default: INFMOE_ROUTE_LAUNCH(8); break;
+    }
+#undef INFMOE_ROUTE_LAUNCH
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
