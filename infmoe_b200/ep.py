@@ -120,12 +120,40 @@ class ExpertParallelMoE:
         dist.all_to_all_single(out, send, output_split_sizes=out_splits, input_split_sizes=in_splits, group=self.group)
         return out
 
+    PHASES = ("local_route_dispatch_scatter", "counts_exchange", "rows_out", "experts", "rows_back", "combine")
+
+    def set_timing(self, enable: bool) -> None:
+        """Record CUDA events between the phases of forward(); read them with phase_ms()."""
+        self._timing = [] if enable else None
+
+    def phase_ms(self):
+        """Average device milliseconds per phase over the timed calls -> dict (empty when timing is off)."""
+        calls = getattr(self, "_timing", None) or []
+        if not calls:
+            return {}
+        torch.cuda.synchronize()
+        tot = [0.0] * len(self.PHASES)
+        for ev in calls:
+            for i in range(len(self.PHASES)):
+                tot[i] += ev[i].elapsed_time(ev[i + 1])
+        return {name: t / len(calls) for name, t in zip(self.PHASES, tot)}
+
     def forward(self, x):
         R, E = self.world, self.expert_count
         per = E // R
+        marks = []
+
+        def mark():
+            if getattr(self, "_timing", None) is not None and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
+
+        mark()
         gate, score = self.stages.route(x)
         count, pos = self.stages.dispatch(gate, E)
         routed, rscore = self.stages.scatter(x, score, pos)
+        mark()
         # counts: what every rank sends to every expert.  recv_counts[src][e_local]
         send_counts = count.view(R, per)
         recv_counts = torch.empty_like(send_counts)
@@ -134,16 +162,24 @@ class ExpertParallelMoE:
         else:
             dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=self.group)
         # the one host synchronisation of the pass: the split sizes of the row exchange
-        send_rows = send_counts.sum(dim=1).cpu().tolist()
-        recv_mat = recv_counts.cpu()
+        both = torch.stack((send_counts, recv_counts)).cpu()
+        send_rows = both[0].sum(dim=1).tolist()
+        recv_mat = both[1]
         recv_rows = recv_mat.sum(dim=1).tolist()
+        mark()
         received = self._all_to_all(routed, recv_rows, send_rows)
+        mark()
         # expert of every received row: rows arrive grouped by (source rank, local expert)
-        local_ids = torch.arange(per, dtype=torch.int32, device=x.device).repeat(R)
-        expert_of_row = torch.repeat_interleave(local_ids, recv_counts.reshape(-1).to(torch.int64),
-                                                output_size=int(sum(recv_rows)))
+        local_ids = torch.arange(per, dtype=torch.int32).repeat(R)
+        expert_of_row = torch.repeat_interleave(local_ids, recv_mat.reshape(-1).to(torch.int64)).to(
+            x.device, non_blocking=True)
         processed = self.stages.experts(received, expert_of_row.contiguous())
+        mark()
         post = self._all_to_all(processed, send_rows, recv_rows)
+        mark()
         out = self.stages.combine(post, routed, rscore, pos)
+        mark()
+        if marks:
+            self._timing.append(marks)
         self.last = {"gate": gate, "score": score, "pos": pos, "count": count, "recv_counts": recv_mat}
         return out

@@ -59,6 +59,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
         moe.forward(dx)
     moe.stages.check()
     local.set_profiling(True)
+    moe.set_timing(True)
     launches0 = local.kernel_launches
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
@@ -72,6 +73,8 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
     launches = torch.tensor([local.kernel_launches - launches0], device=dev, dtype=torch.int64)
     dist.all_reduce(launches, op=dist.ReduceOp.SUM)
     stage_ms, _ = local.stage_ms()
+    phase_ms = moe.phase_ms()
+    moe.set_timing(False)
     local.set_profiling(False)
     moe.stages.check()
 
@@ -116,7 +119,8 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
             "e2e": {"value": T_total / (float(e2e_ms.item()) * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": int(hx.numel() * 4 * world), "d2h_bytes_per_step": int(hout.numel() * 4 * world),
                     "ms_per_step": float(e2e_ms.item())},
-            "gpu_launches": int(launches.item()), "stage_ms_rank0": stage_ms, "rows_received_rank0": received,
+            "gpu_launches": int(launches.item()), "stage_ms_rank0": stage_ms, "phase_ms_rank0": phase_ms,
+            "rows_received_rank0": received,
             "roofline": roofline, "cpu_baseline": None, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
