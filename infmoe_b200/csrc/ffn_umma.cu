@@ -583,8 +583,9 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int r = q * 32 + lane;
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + WBUF_COL;
         const uint8_t* w_ring_ptr = smem_raw + (w_ring - smem_u32(smem_raw));
-        // Software pipeline: while the TMEM stores of k block `it` are in flight, the tile of k block
-        // it + 1 is already read from shared memory (and its slot handed back to the producer).
+        // Software pipeline: the tile of k block it + 1 is read from shared memory and split (and its slot
+        // handed back to the producer) right after the buffer of k block `it` has been handed to the MMA
+        // issuers, i.e. while this warp would otherwise wait for the next TMEM buffer to come free.
         int my_tiles = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) ++my_tiles;
         const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)KB;
@@ -634,14 +635,15 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const uint32_t dst = tlane + (it % WBUFS) * WBUF_STRIDE;
             tmem_st32(dst, hi);
             tmem_st32(dst + BK, pk);
-            // while the stores are in flight: read and split the next tile
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&s_wb_ready[it % PW]));
+            // the next tile is read and split while this buffer is already on its way to the MMA issuers and
+            // the buffer after it is still being consumed
             if (it + 1 < total_it) {
                 ok = fetch(it + 1);
                 if (ok) split();
             }
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(smem_u32(&s_wb_ready[it % PW]));
         }
     }
 
