@@ -269,6 +269,13 @@ __device__ __forceinline__ bool chunk_ends(int kb, int KB) {
     return ((n + 1 + i * (CHUNK_BLOCKS / 2)) % CHUNK_BLOCKS) == 0 || kb + 2 >= KB;
 }
 
+// Tensor maps of the two token planes, one per box height 16, 32, ... 160 rows: a tile's load fetches exactly
+// the rows its MMAs read (n_pad), not the largest tile's worth.
+constexpr int TOKEN_BOXES = 10;
+struct TokenMaps {
+    CUtensorMap hi[TOKEN_BOXES], pk[TOKEN_BOXES];
+};
+
 struct TileInfo {
     int expert, slot, mb, row0, n_tok, n_pad;
 };
@@ -303,9 +310,8 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, c
 
 template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a_hi,
-                const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_hi,
-                const __grid_constant__ CUtensorMap map_b_lo, const GemmArgs args) {
+ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps token_maps,
+                const GemmArgs args) {
     using C = Cfg<NMAX, W_STAGES, T_STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_w_full[W_STAGES];    // TMA -> transform
@@ -408,11 +414,11 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
-                // few tokens: boxes of 32 rows; otherwise one box of NMAX rows per plane (rows past the
-                // chunk belong to the next expert or are zero-filled past the end; the MMA never reads them)
-                const int nbox = (t.n_pad + 31) >> 5;
-                const bool big = 2 * t.n_pad > NMAX;
-                const uint32_t a_bytes = big ? 2 * C::A_TILE : 2 * nbox * 32 * ROW_BYTES;
+                // one box of n_pad rows per plane (rows past the chunk's tokens belong to the next expert or are
+                // zero-filled past the end; they only feed accumulator columns that are never stored)
+                const CUtensorMap* map_hi = &token_maps.hi[(t.n_pad >> 4) - 1];
+                const CUtensorMap* map_pk = &token_maps.pk[(t.n_pad >> 4) - 1];
+                const uint32_t a_bytes = 2 * t.n_pad * ROW_BYTES;
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % T_STAGES;
@@ -424,15 +430,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     mbar_expect_tx(bar, a_bytes);
                     // head plane: 32 floats of the row; packed plane: the row's 64 BF16 of this k block
                     const uint32_t a_hi = a_ring + s * C::A_STAGE, a_pk = a_hi + C::A_TILE;
-                    if (big) {
-                        tma_load_2d(a_hi, &map_b_hi, bar, kb * BK, t.row0);
-                        tma_load_2d(a_pk, &map_b_lo, bar, kb * 2 * BK, t.row0);
-                    } else {
-                        for (int b = 0; b < nbox; ++b) {
-                            tma_load_2d(a_hi + b * 32 * ROW_BYTES, &map_a_hi, bar, kb * BK, t.row0 + b * 32);
-                            tma_load_2d(a_pk + b * 32 * ROW_BYTES, &map_a_lo, bar, kb * 2 * BK, t.row0 + b * 32);
-                        }
-                    }
+                    tma_load_2d(a_hi, map_hi, bar, kb * BK, t.row0);
+                    tma_load_2d(a_pk, map_pk, bar, kb * 2 * BK, t.row0);
                 }
                 if (!ok) break;
             }
@@ -709,22 +708,52 @@ int make_map(CUtensorMap* map, const void* base, uint64_t K, uint64_t rows, uint
     return INFMOE_OK;
 }
 
+// The token maps of a call depend only on the two plane pointers, K and the row count, which repeat from call
+// to call (same workspace): the last few sets are kept per host thread instead of being encoded again.
+int token_maps(TokenMaps* out, const float* a_hi, const float* a_lo, int K, long long T) {
+    struct Entry {
+        const float *hi = nullptr, *lo = nullptr;
+        int K = 0;
+        long long T = 0;
+        TokenMaps maps;
+    };
+    static thread_local Entry cache[4];
+    static thread_local int next = 0;
+    for (const Entry& e : cache)
+        if (e.hi == a_hi && e.lo == a_lo && e.K == K && e.T == T) {
+            *out = e.maps;
+            return INFMOE_OK;
+        }
+    Entry& e = cache[next];
+    next = (next + 1) % 4;
+    e.hi = nullptr;   // stays invalid if an encode fails
+    for (int b = 0; b < TOKEN_BOXES; ++b) {
+        INFMOE_TRY(make_map(&e.maps.hi[b], a_hi, (uint64_t)K, (uint64_t)T, 1, 16 * (b + 1), 2));
+        INFMOE_TRY(make_map(&e.maps.pk[b], a_lo, pack_pitch(K), (uint64_t)T, 1, 16 * (b + 1), 2, true));
+    }
+    e.hi = a_hi;
+    e.lo = a_lo;
+    e.K = K;
+    e.T = T;
+    *out = e.maps;
+    return INFMOE_OK;
+}
+
 template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
 int launch_one(const GemmArgs& args, long long T, int slots, const float* w, const float* a_hi, const float* a_lo,
                int num_ctas, cudaStream_t stream) {
     using C = Cfg<NMAX, W_STAGES, T_STAGES>;
     static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory rings too large");
-    CUtensorMap m[5];
+    static_assert(NMAX <= 16 * TOKEN_BOXES, "a token tile needs a tensor map of its height");
+    CUtensorMap map_w;
+    TokenMaps tm;
     // weights: tile-contiguous plane = a [slots * MB * KB * 128][32] matrix, one 16 KB tile per box
     const uint64_t w_rows = (uint64_t)slots * ((args.M_total + UMMA_M - 1) / UMMA_M) * ((args.K + BK - 1) / BK) * UMMA_M;
-    INFMOE_TRY(make_map(&m[0], w, BK, w_rows, 1, UMMA_M, 2));
-    INFMOE_TRY(make_map(&m[1], a_hi, args.K, (uint64_t)T, 1, 32, 2));
-    INFMOE_TRY(make_map(&m[2], a_lo, pack_pitch(args.K), (uint64_t)T, 1, 32, 2, true));
-    INFMOE_TRY(make_map(&m[3], a_hi, args.K, (uint64_t)T, 1, NMAX, 2));
-    INFMOE_TRY(make_map(&m[4], a_lo, pack_pitch(args.K), (uint64_t)T, 1, NMAX, 2, true));
+    INFMOE_TRY(make_map(&map_w, w, BK, w_rows, 1, UMMA_M, 2));
+    INFMOE_TRY(token_maps(&tm, a_hi, a_lo, args.K, T));
     auto kern = ffn_umma_kernel<EPI, NMAX, W_STAGES, T_STAGES>;
     INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(m[0], m[1], m[2], m[3], m[4], args);
+    kern<<<num_ctas, GEMM_THREADS, C::SMEM, stream>>>(map_w, tm, args);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
