@@ -130,6 +130,14 @@ __device__ __forceinline__ void store_pack4(uint16_t* __restrict__ pack_row, int
     *reinterpret_cast<uint2*>(g + 32) = make_uint2(pack_bf16x2(lo[0], lo[1]), pack_bf16x2(lo[2], lo[3]));
 }
 
+// base_layer output mix (plugin/cuda/moe.cu:115-127, sigmoid plugin/cuda/common.cuh:24-27):
+// out = alpha * expert_output + (1 - alpha) * input with alpha = sigmoid(score).  One fixed rounding sequence, so
+// that the stand-alone combine kernel and the GEMM epilogue that fuses it give the same bits.
+__device__ __forceinline__ float mix_alpha(float score) { return 1.0f / (1.0f + expf(-score)); }
+__device__ __forceinline__ float mix_value(float alpha, float beta, float post, float routed) {
+    return __fmaf_rn(alpha, post, __fmul_rn(beta, routed));
+}
+
 // gelu(a) * b in the reference's evaluation order (plugin/cuda/ops/gelu.cu:8-15).
 __device__ __forceinline__ float gelu_dot(float a, float b) {
     const float cdf = 0.5f * (1.0f + tanhf(a * (0.035677408136300125f * a * a + 0.7978845608028654f)));

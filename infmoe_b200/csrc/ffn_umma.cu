@@ -258,6 +258,9 @@ struct GemmArgs {
     float* out_hi;              // GELU_PAIR: g_hi [T][M_total / 2]; RESIDUAL: y [T][M_total]
     float* out_lo;              // GELU_PAIR: g_lo
     const float* resid;         // RESIDUAL: x [T][M_total]
+    const int* out_pos;         // RESIDUAL: row j is written to row out_pos[j] of y (NULL: row j), i.e. the combine
+                                // step moe_expert_gather (plugin/cuda/moe.cu:89-96) fused into the epilogue
+    const float* mix_score;     // RESIDUAL: routed scores for the base_layer output mix (NULL: no mix)
     int* status;
 };
 
@@ -566,8 +569,16 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         }
                     } else {
                         if (col < t.n_tok && m_ok) {
-                            const size_t o = (size_t)(t.row0 + col) * (size_t)args.M_total + (size_t)m;
-                            args.out_hi[o] = __fadd_rn(args.resid[o], v);
+                            const int row = t.row0 + col;
+                            const size_t o = (size_t)row * (size_t)args.M_total + (size_t)m;
+                            const float x = args.resid[o];
+                            float y = __fadd_rn(x, v);
+                            if (args.mix_score) {
+                                const float alpha = mix_alpha(args.mix_score[row]);
+                                y = mix_value(alpha, 1.0f - alpha, y, x);
+                            }
+                            const size_t oo = args.out_pos ? (size_t)args.out_pos[row] * (size_t)args.M_total + (size_t)m : o;
+                            args.out_hi[oo] = y;
                         }
                     }
                 }
@@ -773,7 +784,8 @@ bool ffn_umma_supported(int D, int F, int E) {
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
                     const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
                     const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
-                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event) {
+                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event, const int* out_pos,
+                    const float* mix_score) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     if (!ffn_umma_supported(D, F, E)) {
         set_error("ffn_umma: unsupported shape D=%d F=%d E=%d", D, F, E);
@@ -797,6 +809,8 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a2.out_hi = post;
     a2.out_lo = nullptr;
     a2.resid = routed;
+    a2.out_pos = out_pos;
+    a2.mix_score = mix_score;
     // Shapes: token chunk, weight stages (16 KB each), token stages.  INFMOE_GEMM_TILE selects another instantiation
     // for tuning runs.
     static const int variant = [] {

@@ -42,9 +42,12 @@ int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int
                     float* g_hi, float* g_lo, float* post, cudaStream_t stream);
 
 bool ffn_umma_supported(int D, int F, int E);
+// out_pos != NULL: `post` is the layer output in token order, row j of the experts' result goes to row out_pos[j]
+// (and mix_score != NULL applies the base_layer output mix on the way): the combine step fused into the epilogue.
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
                     const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
                     const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
-                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event = nullptr);
+                    int num_sms, cudaStream_t stream, cudaEvent_t mid_event = nullptr, const int* out_pos = nullptr,
+                    const float* mix_score = nullptr);
 
 }  // namespace infmoe

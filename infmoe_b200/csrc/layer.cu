@@ -350,13 +350,25 @@ int status_to_rc(int status) {
     return INFMOE_OK;
 }
 
+// Where the experts' result goes: `post` in expert order (a combine kernel follows), or, on the tensor-core path,
+// straight into the layer output in token order (`out` with the row map `pos`, optionally the base_layer mix).
+struct FfnOutput {
+    float* post;
+    float* out = nullptr;
+    const int* pos = nullptr;
+    const float* mix_score = nullptr;
+};
+
+bool uses_umma(const infmoe_layer* L) { return L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E); }
+
 int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_offset, const int* d_slot_map,
             int slots, float* const planes[2], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
-            float* g_lo, float* post, cudaStream_t stream, cudaEvent_t mid = nullptr) {
-    const bool umma = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);
-    if (umma)
+            float* g_lo, const FfnOutput& o, cudaStream_t stream, cudaEvent_t mid = nullptr) {
+    if (uses_umma(L))
         return launch_ffn_umma(T, L->D, L->F, L->E, e_begin, e_end, d_offset, d_slot_map, slots, h_hi, h_lo, planes[0],
-                               planes[1], routed, g_hi, g_lo, post, L->d_status, L->num_sms, stream, mid);
+                               planes[1], routed, g_hi, g_lo, o.out ? o.out : o.post, L->d_status, L->num_sms, stream,
+                               mid, o.out ? o.pos : nullptr, o.out ? o.mix_score : nullptr);
+    float* post = o.post;
     return launch_ffn_simt(T, L->D, L->F, e_begin, e_end, d_offset, d_slot_map, h_hi, h_lo, planes[0], planes[1],
                            routed, g_hi, g_lo, post, stream);
 }
@@ -809,13 +821,23 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     // 2. dispatch metadata (:350-352)
     INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 2, stream));
+    const bool mix = L->flags.base_layer_mix && !given_gate;
+    // the tensor-core GEMM writes the layer output itself (combine fused into its epilogue)
+    const bool fused_combine = !L->identity && uses_umma(L);
+    FfnOutput ffn_out;
+    ffn_out.post = post;
+    if (fused_combine) {
+        ffn_out.out = d_out;
+        ffn_out.pos = pos;
+        ffn_out.mix_score = mix ? rscore : nullptr;
+    }
     if (L->identity) {
         // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
         INFMOE_TRY(launch_scatter(T, L->D, d_in, score, pos, routed, rscore, stream));
         INFMOE_CUDA_TRY(cudaMemcpyAsync(post, routed, sizeof(float) * (size_t)T * L->D, cudaMemcpyDeviceToDevice, stream));
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
-        const bool pack = L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E);   // the GEMM run_ffn picks
+        const bool pack = uses_umma(L);   // the GEMM run_ffn picks
         INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate_in, s->d_ln, routed, rscore, h_hi, h_lo,
                                            pack, stream));
         INFMOE_TRY(prof_mark(L, 3, stream));
@@ -823,8 +845,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
         if (!streamed) {
             cudaEvent_t mid = nullptr;
             if (L->profiling) mid = L->prof_events[(size_t)(L->prof_calls % PROF_CALLS) * PROF_MARKS + 4];
-            INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, nullptr, L->E, s->d_plane, h_hi, h_lo, routed, g_hi, g_lo, post,
-                               stream, mid));
+            INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, nullptr, L->E, s->d_plane, h_hi, h_lo, routed, g_hi, g_lo,
+                               ffn_out, stream, mid));
         } else {
             const size_t n = s->matrix_elems();
             // slot planes: w01 [mc] x tiled(2F x D), wo [mc] x tiled(D x F), then one raw landing area per slot
@@ -873,8 +895,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
             if (all_cached) {
                 // nothing to copy: one grouped launch over all experts, as in resident mode
                 for (const CachePlan& pl : plan) INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[pl.slot], 0));
-                INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, slot_map, nslots, planes, h_hi, h_lo, routed, g_hi, g_lo, post,
-                                   stream));
+                INFMOE_TRY(run_ffn(L, T, 0, L->E, offset, slot_map, nslots, planes, h_hi, h_lo, routed, g_hi, g_lo,
+                                   ffn_out, stream));
                 for (const CachePlan& pl : plan) INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[pl.slot], stream));
             }
             for (size_t j = 0; j < active.size() && !all_cached; ++j) {
@@ -899,15 +921,16 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                 }
                 INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
                 INFMOE_TRY(run_ffn(L, T, e, e + 1, offset, slot_map, nslots, planes, h_hi, h_lo, routed, g_hi, g_lo,
-                                   post, stream));
+                                   ffn_out, stream));
                 INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[slot], stream));
             }
             INFMOE_TRY(prof_mark(L, 4, stream));   // streamed: copies and both GEMMs are timed together
         }
     }
     INFMOE_TRY(prof_mark(L, 5, stream));
-    // 5. combine (:407-412; the gather reads the expert output)
-    if (L->flags.base_layer_mix && !given_gate)
+    // 5. combine (:407-412; the gather reads the expert output), unless the GEMM epilogue has done it
+    if (fused_combine) {
+    } else if (mix)
         INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, d_out, stream));
     else
         INFMOE_TRY(launch_gather(T, L->D, post, pos, d_out, stream));
@@ -973,8 +996,23 @@ int infmoe_layer_forward_host(infmoe_layer* L, const float* h_in, float* h_out, 
         L->own_ws_bytes = need;
     }
     INFMOE_CUDA_TRY(cudaMemcpyAsync(L->own_in, h_in, io, cudaMemcpyHostToDevice, L->own_stream));
-    INFMOE_TRY(infmoe_layer_enqueue(L, L->own_in, L->own_out, L->own_ws, L->own_ws_bytes, T, L->own_stream));
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, L->own_out, io, cudaMemcpyDeviceToHost, L->own_stream));
+    // Page-locked output buffers are written by the last kernel of the layer itself (with the combine fused into
+    // the second GEMM the rows cross PCIe while the GEMM is still running); pageable ones get a copy afterwards.
+    float* direct = nullptr;
+    static const bool allow_direct = [] {
+        const char* v = getenv("INFMOE_DIRECT_HOST_OUTPUT");
+        return !(v && atoi(v) == 0);
+    }();
+    if (allow_direct && !L->identity && uses_umma(L)) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, h_out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+            direct = (float*)attr.devicePointer;
+        else
+            (void)cudaGetLastError();
+    }
+    INFMOE_TRY(infmoe_layer_enqueue(L, L->own_in, direct ? direct : L->own_out, L->own_ws, L->own_ws_bytes, T,
+                                    L->own_stream));
+    if (!direct) INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, L->own_out, io, cudaMemcpyDeviceToHost, L->own_stream));
     return infmoe_layer_sync_status(L, L->own_stream);
 }
 

@@ -108,7 +108,7 @@ mix_gather_kernel(long long T, int D, int vec, const int* __restrict__ pos, cons
     const int lane = threadIdx.x & 31;
     const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
     if (j >= T) return;
-    const float alpha = 1.0f / (1.0f + expf(-coeff[j]));
+    const float alpha = mix_alpha(coeff[j]);
     const float beta = 1.0f - alpha;
     const float* a = post + j * D;
     const float* b = routed + j * D;
@@ -118,14 +118,14 @@ mix_gather_kernel(long long T, int D, int vec, const int* __restrict__ pos, cons
             const float4 x = reinterpret_cast<const float4*>(a)[i];
             const float4 y = reinterpret_cast<const float4*>(b)[i];
             float4 r;
-            r.x = alpha * x.x + beta * y.x;
-            r.y = alpha * x.y + beta * y.y;
-            r.z = alpha * x.z + beta * y.z;
-            r.w = alpha * x.w + beta * y.w;
+            r.x = mix_value(alpha, beta, x.x, y.x);
+            r.y = mix_value(alpha, beta, x.y, y.y);
+            r.z = mix_value(alpha, beta, x.z, y.z);
+            r.w = mix_value(alpha, beta, x.w, y.w);
             reinterpret_cast<float4*>(o)[i] = r;
         }
     } else {
-        for (int i = lane; i < D; i += 32) o[i] = alpha * a[i] + beta * b[i];
+        for (int i = lane; i < D; i += 32) o[i] = mix_value(alpha, beta, a[i], b[i]);
     }
 }
 

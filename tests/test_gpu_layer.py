@@ -150,6 +150,22 @@ def test_expert_cache_keeps_experts_across_calls(torch_cuda, oracle, tmp_path, s
     st.terminate()
 
 
+@pytest.mark.parametrize("variant", ["cpm_2", "base_layer"])
+def test_forward_host_into_page_locked_output(torch_cuda, oracle, variant):
+    """A page-locked output buffer is written by the layer's last kernel directly; same bits as the copied path."""
+    from infmoe_b200 import synth
+    torch = torch_cuda
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=6, embedding_size=128, hidden_size=256,
+                     batch=1, seq_len=200)
+    layer, x, c, ln, experts = _build(w, synth, from_npz=False)
+    want = _check(layer, w, x, c, ln, experts, oracle, torch)          # pageable numpy output
+    hx = torch.from_numpy(x).pin_memory()
+    hout = torch.full_like(hx, float("nan")).pin_memory()
+    layer.forward_host_ptr(hx.data_ptr(), hout.data_ptr(), w.tokens)
+    np.testing.assert_array_equal(hout.numpy(), want)
+    layer.terminate()
+
+
 def test_exact_path_matches_tensor_core_path(torch_cuda, oracle, monkeypatch):
     from infmoe_b200 import synth
     w = synth.scaled(synth.WORKLOADS["base_layer_zipf"], expert_count=8, embedding_size=128, hidden_size=256, batch=2,
