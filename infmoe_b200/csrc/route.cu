@@ -6,9 +6,11 @@
 //   cublasSgemm_v2       plugin/MoELayerPlugin.cc:334-336  (aff = Xs * C^T)
 //   moe_expert_select    plugin/cuda/moe.cu:147-159     (strict '>' scan, first maximum wins)
 //
-// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA of WARPS warps owns
-// 4 * WARPS tokens (TPW = 4 per warp; WARPS is picked per launch so that the CTAs fill
-// whole waves of the SMs).  The rows of X are read from global memory one 128-float step
+// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA owns 4 * TW tokens (TPW = 4 per
+// warp; TW token warps, picked per launch so that the CTAs fill whole waves of the SMs).  With more
+// than one group of EG experts the CTA has two such sets of warps ("halves"): both work on the same
+// tokens, half h takes the expert groups h, h + 2, ..., and their winners are merged at the end, which
+// doubles the warps that hide each other's latencies.  The rows of X are read from global memory one 128-float step
 // ahead of their use.  Centroids are streamed through shared memory in
 // tiles of EG experts x KT floats with double-buffered cp.async, so every
 // centroid byte is fetched from L2 once per CTA and every LDS.128 feeds
@@ -34,32 +36,37 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Fills one shared-memory tile: experts [e0, e0+EG) x floats [k0, k0+KT) of the centroids, zero padded.
 template <int EG, int KT, int ROUTE_THREADS>
 __device__ __forceinline__ void load_centroid_tile(float* __restrict__ tile, const float* __restrict__ C, int E, int D,
-                                                   int e0, int k0, bool vec) {
+                                                   int e0, int k0, bool vec, int tid) {
     if (vec) {
-        for (int idx = threadIdx.x; idx < EG * (KT / 4); idx += ROUTE_THREADS) {
+        for (int idx = tid; idx < EG * (KT / 4); idx += ROUTE_THREADS) {
             const int j = idx / (KT / 4), k = (idx % (KT / 4)) * 4;
             float* dst = tile + j * KT + k;
             if (e0 + j < E && k0 + k < D) cp_async16(dst, C + (long long)(e0 + j) * D + k0 + k);
             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     } else {
-        for (int idx = threadIdx.x; idx < EG * KT; idx += ROUTE_THREADS) {
+        for (int idx = tid; idx < EG * KT; idx += ROUTE_THREADS) {
             const int j = idx / KT, k = idx % KT;
             tile[idx] = (e0 + j < E && k0 + k < D) ? C[(long long)(e0 + j) * D + k0 + k] : 0.f;
         }
     }
 }
 
-template <int TPW, int EG, int KT, int ROUTE_WARPS>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+template <int TPW, int EG, int KT, int TW, int HALVES>
+__global__ void __launch_bounds__(TW * HALVES * 32)
 route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
              long long T, int D, int E, int vec, int* __restrict__ gate, float* __restrict__ score,
              int* __restrict__ status) {
-    constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
-    extern __shared__ __align__(16) float s_tiles[];   // [2][EG][KT]
+    constexpr int HALF_THREADS = TW * 32;
+    extern __shared__ __align__(16) float s_all_tiles[];   // [HALVES][2][EG][KT]
+    __shared__ float s_merge_score[TW][TPW];
+    __shared__ int s_merge_e[TW][TPW];
     const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const long long t0 = ((long long)blockIdx.x * ROUTE_WARPS + warp) * TPW;
+    const int half = (threadIdx.x >> 5) / TW;          // which set of expert groups this warp works on
+    const int warp = (threadIdx.x >> 5) % TW;          // which tokens
+    const int tid = threadIdx.x - half * HALF_THREADS; // thread index inside the half (tile loads)
+    float* const s_tiles = s_all_tiles + half * 2 * EG * KT;
+    const long long t0 = ((long long)blockIdx.x * TW + warp) * TPW;
     const bool warp_live = t0 < T;   // whole warps past the end still help loading tiles
 
     const float* rows[TPW];
@@ -98,47 +105,48 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         }
     };
     fetch(4 * lane);
-    for (int e0 = 0; e0 < E; e0 += EG) {
+    // both halves run the same number of group passes (they share the CTA-wide barriers); a pass past the last
+    // group loads zero tiles and selects nothing
+    const int groups = (E + EG - 1) / EG, passes = (groups + HALVES - 1) / HALVES;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int e0 = (pass * HALVES + half) * EG;
         float acc[TPW][EG];
 #pragma unroll
         for (int i = 0; i < TPW; ++i)
 #pragma unroll
             for (int j = 0; j < EG; ++j) acc[i][j] = 0.f;
 
-        load_centroid_tile<EG, KT, ROUTE_THREADS>(s_tiles, C, E, D, e0, 0, vec != 0);
+        load_centroid_tile<EG, KT, HALF_THREADS>(s_tiles, C, E, D, e0, 0, vec != 0, tid);
         cp_async_commit();
         for (int kt = 0; kt < ntiles; ++kt) {
             const float* tile = s_tiles + (kt & 1) * EG * KT;
             if (kt + 1 < ntiles)
-                load_centroid_tile<EG, KT, ROUTE_THREADS>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT,
-                                                          vec != 0);
+                load_centroid_tile<EG, KT, HALF_THREADS>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT,
+                                                         vec != 0, tid);
             cp_async_commit();
             cp_async_wait<1>();   // tile kt has landed (the group of tile kt+1 may still be in flight)
             __syncthreads();
-            if (warp_live) {
+            if (warp_live && e0 < E) {
 #pragma unroll 1   // one step is 256 FMAs per lane; unrolling further only thrashes the instruction cache
                 for (int it = 0; it < KT / 128; ++it) {
                     const int kl = it * 128 + 4 * lane;       // offset inside the tile
                     const int base = kt * KT + kl;            // offset inside the row
-                    float4 v_cur[TPW];
+                    // this step's values (normalised if asked for) leave v_next before the next fetch overwrites it
+                    float xs[TPW][4];
 #pragma unroll
-                    for (int i = 0; i < TPW; ++i) v_cur[i] = v_next[i];
-                    const float4 g4 = g_next;
+                    for (int i = 0; i < TPW; ++i) {
+                        const float4 v = v_next[i];
+                        if (use_ln) {
+                            xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g_next.x);
+                            xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g_next.y);
+                            xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g_next.z);
+                            xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g_next.w);
+                        } else {
+                            xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
+                        }
+                    }
                     fetch(base + 128 < ntiles * KT ? base + 128 : 4 * lane);
                     if (base < D) {
-                        float xs[TPW][4];
-#pragma unroll
-                        for (int i = 0; i < TPW; ++i) {
-                            const float4 v = v_cur[i];
-                            if (use_ln) {
-                                xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g4.x);
-                                xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g4.y);
-                                xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g4.z);
-                                xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g4.w);
-                            } else {
-                                xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
-                            }
-                        }
                         const int nvalid = min(4, D - base);
 #pragma unroll
                         for (int j = 0; j < EG; ++j) {
@@ -171,7 +179,30 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
             }
         }
     }
-    if (lane == 0 && warp_live) {
+    if (HALVES > 1) {
+        // merge the halves' winners: highest score, lowest expert index among equal scores -- the expert the
+        // reference's sequential strict '>' scan would have kept
+        if (half == 1 && lane == 0) {
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+                s_merge_score[warp][i] = best[i];
+                s_merge_e[warp][i] = best_e[i];
+            }
+        }
+        __syncthreads();
+        if (half == 0) {
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+                const float so = s_merge_score[warp][i];
+                const int eo = s_merge_e[warp][i];
+                if (eo >= 0 && (best_e[i] < 0 || so > best[i] || (so == best[i] && eo < best_e[i]))) {
+                    best[i] = so;
+                    best_e[i] = eo;
+                }
+            }
+        }
+    }
+    if (lane == 0 && warp_live && half == 0) {
 #pragma unroll
         for (int i = 0; i < TPW; ++i) {
             if (!live[i]) continue;
@@ -237,9 +268,10 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
         INFMOE_CUDA_TRY(cudaGetDevice(&dev));
         INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     }
-    int warps = 8;
+    const int halves = E > EG / 2 ? 2 : 1;
+    int warps = 7;
     long long best_cost = -1;
-    for (int w = 8; w >= 5; --w) {
+    for (int w = (halves == 2 ? 7 : 8); w >= 5; --w) {
         const long long ctas = (T + (long long)w * TPW - 1) / ((long long)w * TPW);
         const long long cost = ((ctas + sms - 1) / sms) * w;
         if (best_cost < 0 || cost < best_cost) {
@@ -248,17 +280,21 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
         }
     }
     const long long grid = (T + (long long)warps * TPW - 1) / ((long long)warps * TPW);
-#define INFMOE_ROUTE_LAUNCH(W)                                                                                     \
+#define INFMOE_ROUTE_LAUNCH(W, H)                                                                                  \
     do {                                                                                                           \
-        auto kern = route_kernel<TPW, EG, KT, W>;                                                                  \
+        /* two halves: 8 experts per group and half, so that the accumulators of 448 threads fit the register file */ \
+        auto kern = route_kernel<TPW, EG / H, KT, W, H>;                                                           \
         INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));            \
-        kern<<<(unsigned)grid, W * 32, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status);     \
+        kern<<<(unsigned)grid, W * H * 32, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status); \
     } while (0)
-    switch (warps) {
-        case 5: INFMOE_ROUTE_LAUNCH(5); break;
-        case 6: INFMOE_ROUTE_LAUNCH(6); break;
-        case 7: INFMOE_ROUTE_LAUNCH(7); break;
-        default: INFMOE_ROUTE_LAUNCH(8); break;
+    switch (warps * 10 + halves) {
+        case 51: INFMOE_ROUTE_LAUNCH(5, 1); break;
+        case 61: INFMOE_ROUTE_LAUNCH(6, 1); break;
+        case 71: INFMOE_ROUTE_LAUNCH(7, 1); break;
+        case 81: INFMOE_ROUTE_LAUNCH(8, 1); break;
+        case 52: INFMOE_ROUTE_LAUNCH(5, 2); break;
+        case 62: INFMOE_ROUTE_LAUNCH(6, 2); break;
+        default: INFMOE_ROUTE_LAUNCH(7, 2); break;
     }
 #undef INFMOE_ROUTE_LAUNCH
     note_launch();
