@@ -114,6 +114,8 @@ def cpu_sample_setup(w: synth.Workload, sample_experts: int, tokens_per_expert: 
     """A bounded slice of workload `w`: `sample_experts` experts and the tokens they would get."""
     from oracle import oracle
 
+    # all host cores, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for every rank)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     ws = synth.scaled(w, expert_count=sample_experts, batch=1, seq_len=sample_experts * tokens_per_expert)
     x, cent, ln = synth.gen_inputs(ws)
     experts = [synth.gen_expert_numpy(ws, e) for e in range(sample_experts)]
