@@ -147,17 +147,17 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
                     }
                     fetch(base + 128 < ntiles * KT ? base + 128 : 4 * lane);
                     if (base < D) {
-                        const int nvalid = min(4, D - base);
+                        // Positions past the end of a row (D not a multiple of 4) hold zeros in the centroid tile and
+                        // a zero gamma or zero x: their products are exact zeros and leave the partial sums'
+                        // bits unchanged, so they need no predicate.
 #pragma unroll
                         for (int j = 0; j < EG; ++j) {
                             const float4 c = *reinterpret_cast<const float4*>(tile + j * KT + kl);
                             const float cc[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
-                                if (k < nvalid) {
 #pragma unroll
-                                    for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
-                                }
+                                for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
                             }
                         }
                     }
