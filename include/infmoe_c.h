@@ -96,6 +96,12 @@ INFMOE_API int infmoe_layer_set_residency(infmoe_layer* layer, int mode);
  * loop that keeps hitting the same experts stops paying for the host->device copies; slots = 0 (default): off.
  * Device memory: slots x 12 * d_model * d_ff bytes, allocated at the next streamed enqueue. */
 INFMOE_API int infmoe_layer_set_expert_cache(infmoe_layer* layer, int32_t slots);
+/* Host-only companion of the expert cache (no GPU needed, no counterpart in the reference): replays `calls`
+ * enqueue calls against a cache of `slots` slots with the layer's own replacement policy and reports how many
+ * experts each call would have to copy.  experts: the active expert ids of all calls back to back, ascending
+ * inside a call; call_sizes[c]: how many of them belong to call c.  For sizing the cache from a routing trace. */
+INFMOE_API int infmoe_expert_cache_simulate(int32_t slots, int32_t expert_count, const int32_t* experts,
+                                            const int32_t* call_sizes, int32_t calls, int32_t* loads_per_call);
 /* Expert weight bytes enqueue has copied host -> device for this layer object so far (streamed mode). */
 INFMOE_API int infmoe_layer_weight_h2d_bytes(const infmoe_layer* layer, uint64_t* bytes);
 

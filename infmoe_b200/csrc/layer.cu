@@ -738,6 +738,38 @@ std::vector<CachePlan> plan_cache(infmoe_layer* L, const std::vector<int>& activ
 
 }  // namespace
 
+int infmoe_expert_cache_simulate(int32_t slots, int32_t expert_count, const int32_t* experts, const int32_t* call_sizes,
+                                 int32_t calls, int32_t* loads_per_call) {
+    if (slots <= 0 || expert_count <= 0 || calls < 0 || (calls > 0 && (!experts || !call_sizes || !loads_per_call))) {
+        set_error("expert_cache_simulate: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    // the layer's own planning code on a layer object without device state
+    infmoe_layer L;
+    L.E = expert_count;
+    L.store = make_store(expert_count, 1, 1);
+    L.cache_slots = slots;
+    L.cache_expert.assign(slots, -1);
+    L.cache_version.assign(slots, 0);
+    L.cache_used.assign(slots, 0);
+    L.cache_slot_of.assign(expert_count, -1);
+    const int32_t* p = experts;
+    for (int32_t c = 0; c < calls; ++c) {
+        std::vector<int> active;
+        for (int32_t i = 0; i < call_sizes[c]; ++i, ++p) {
+            if (*p < 0 || *p >= expert_count || (!active.empty() && *p <= active.back())) {
+                set_error("expert_cache_simulate: call %d: expert ids must be ascending and inside [0, %d)", c, expert_count);
+                return INFMOE_ERR_INVALID_ARGUMENT;
+            }
+            active.push_back(*p);
+        }
+        int loads = 0;
+        for (const CachePlan& pl : plan_cache(&L, active)) loads += pl.load ? 1 : 0;
+        loads_per_call[c] = loads;
+    }
+    return INFMOE_OK;
+}
+
 int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes) {
     if (!L || !bytes || T < 0) {
         set_error("layer_workspace_bytes: bad argument");

@@ -80,9 +80,30 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         rstd[i] = 1.f;
     }
     const bool use_ln = gamma != nullptr;
-    if (use_ln && warp_live) {
+    if (use_ln) {
+        // row statistics once per token: half 0 computes them, the other half reads them from shared memory
+        if (warp_live && half == 0) {
 #pragma unroll
-        for (int i = 0; i < TPW; ++i) warp_row_stats(rows[i], D, vec != 0, mean[i], rstd[i]);
+            for (int i = 0; i < TPW; ++i) warp_row_stats(rows[i], D, vec != 0, mean[i], rstd[i]);
+        }
+        if (HALVES > 1) {
+            __shared__ float s_mean[TW][TPW], s_rstd[TW][TPW];
+            if (half == 0 && lane == 0) {
+#pragma unroll
+                for (int i = 0; i < TPW; ++i) {
+                    s_mean[warp][i] = mean[i];
+                    s_rstd[warp][i] = rstd[i];
+                }
+            }
+            __syncthreads();
+            if (half != 0) {
+#pragma unroll
+                for (int i = 0; i < TPW; ++i) {
+                    mean[i] = s_mean[warp][i];
+                    rstd[i] = s_rstd[warp][i];
+                }
+            }
+        }
     }
 
     float best[TPW];

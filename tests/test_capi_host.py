@@ -160,3 +160,40 @@ def test_enqueue_without_gpu_fails_loudly():
         layer.forward_host(np.zeros((4, 8), np.float32))
     assert e.value.status in (2, 6, 8)
     layer.terminate()
+
+
+def _simulate(slots, E, calls):
+    import ctypes
+
+    import numpy as np
+    from infmoe_b200 import capi
+    flat = np.asarray([e for c in calls for e in c], np.int32)
+    sizes = np.asarray([len(c) for c in calls], np.int32)
+    loads = np.zeros(len(calls), np.int32)
+    capi.check(capi.lib().infmoe_expert_cache_simulate(slots, E, flat.ctypes.data, sizes.ctypes.data, len(calls),
+                                                       loads.ctypes.data))
+    return loads.tolist()
+
+
+def test_expert_cache_policy_on_the_host():
+    """The replacement policy of the streamed mode's expert cache, replayed without a GPU."""
+    # everything fits: each expert is copied once
+    assert _simulate(4, 8, [[0, 1, 2], [1, 2, 3], [0, 3], [0, 1, 2, 3]]) == [3, 1, 0, 0]
+    # least recently used goes first: after [0,1] [2,3] [0], expert 1 is the oldest and is replaced by 4
+    assert _simulate(4, 8, [[0, 1], [2, 3], [0], [4], [0, 2, 3, 4], [1]]) == [2, 2, 0, 1, 0, 1]
+    # a repeating call larger than the cache: plain LRU would never hit; keeping the slots that later experts of
+    # the same call are about to use saves one copy per call
+    assert _simulate(2, 8, [[0, 1, 2]] * 3) == [3, 2, 2]
+    # a call larger than the cache keeps what it can: slots reserved by later hits are not taken by earlier misses
+    assert _simulate(3, 8, [[5, 6, 7], [0, 5, 6, 7]]) == [3, 2]   # expert 7, needed last, gives its slot to 0 and is reloaded
+    # one slot more and only the new expert is copied
+    assert _simulate(4, 8, [[5, 6, 7], [0, 5, 6, 7]]) == [3, 1]
+
+
+def test_expert_cache_simulate_rejects_bad_input():
+    import pytest
+    from infmoe_b200 import capi
+    with pytest.raises(capi.InfMoEError):
+        _simulate(2, 4, [[1, 0]])        # not ascending
+    with pytest.raises(capi.InfMoEError):
+        _simulate(2, 4, [[0, 4]])        # out of range
