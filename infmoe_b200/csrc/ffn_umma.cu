@@ -555,10 +555,22 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             for (int i = 0; i < C::SLICES; ++i) {
                 const int sl = 2 * i + half;
                 if (sl >= nsl) continue;     // uniform across the warp
+                // RESIDUAL: output row and mix coefficient of the slice's 16 token columns, one column per lane
+                // (lanes 16..31 repeat them), handed out by shuffle below
+                int lane_row = 0;
+                float lane_alpha = 0.f;
+                if (EPI == EPI_RESIDUAL) {
+                    const int lc = sl * 16 + (lane & 15);
+                    const int r = t.row0 + lc;
+                    lane_row = (lc < t.n_tok && args.out_pos) ? args.out_pos[r] : r;
+                    if (args.mix_score && lc < t.n_tok) lane_alpha = mix_alpha(args.mix_score[r]);
+                }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const int col = sl * 16 + c;
                     const float v = sum[i][c];
+                    const int out_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_row, c) : 0;
+                    const float alpha = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_alpha, c) : 0.f;
                     if (EPI == EPI_GELU_PAIR) {
                         // even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
@@ -585,12 +597,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             const size_t o = (size_t)row * (size_t)args.M_total + (size_t)m;
                             const float x = args.resid[o];
                             float y = __fadd_rn(x, v);
-                            if (args.mix_score) {
-                                const float alpha = mix_alpha(args.mix_score[row]);
-                                y = mix_value(alpha, 1.0f - alpha, y, x);
-                            }
-                            const size_t oo = args.out_pos ? (size_t)args.out_pos[row] * (size_t)args.M_total + (size_t)m : o;
-                            args.out_hi[oo] = y;
+                            if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
+                            args.out_hi[(size_t)out_row * (size_t)args.M_total + (size_t)m] = y;
                         }
                     }
                 }
