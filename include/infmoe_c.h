@@ -96,6 +96,12 @@ INFMOE_API int infmoe_layer_set_residency(infmoe_layer* layer, int mode);
  * loop that keeps hitting the same experts stops paying for the host->device copies; slots = 0 (default): off.
  * Device memory: slots x 12 * d_model * d_ff bytes, allocated at the next streamed enqueue. */
 INFMOE_API int infmoe_layer_set_expert_cache(infmoe_layer* layer, int32_t slots);
+/* Diagnostic, no counterpart in the reference: launches one warp that waits on a barrier nothing completes,
+ * through the bounded wait every role of the expert GEMM uses, with a limit of limit_ms (1..2000) instead of the
+ * GEMM's 4 s.  timed_out = 1 when the wait gave up and raised the status bit that infmoe_layer_sync_status
+ * reports as INFMOE_ERR_DEVICE_TIMEOUT; waited_ms = how long the warp waited.  The context stays usable. */
+INFMOE_API int infmoe_wait_timeout_probe(uint32_t limit_ms, int32_t* timed_out, float* waited_ms);
+
 /* Host-only companion of the expert cache (no GPU needed, no counterpart in the reference): replays `calls`
  * enqueue calls against a cache of `slots` slots with the layer's own replacement policy and reports how many
  * experts each call would have to copy.  experts: the active expert ids of all calls back to back, ascending

@@ -62,6 +62,7 @@ SIGNATURES = {
     "infmoe_layer_set_expert_cache": [_vp, _i32],
     "infmoe_layer_weight_h2d_bytes": [_vp, ctypes.POINTER(ctypes.c_uint64)],
     "infmoe_expert_cache_simulate": [_i32, _i32, _vp, _vp, _i32, _vp],
+    "infmoe_wait_timeout_probe": [ctypes.c_uint32, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float)],
     "infmoe_layer_workspace_bytes": [_vp, _i64, ctypes.POINTER(_sz)],
     "infmoe_layer_enqueue": [_vp, _vp, _vp, _vp, _sz, _i64, _vp],
     "infmoe_layer_expert_forward": [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _vp],

@@ -131,17 +131,21 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parit
 // Bounded wait.  Returns false when the wait was abandoned (limit reached here or in another role).
 // The slow path is a real function call (about 200 cycles on B200); the common case, a barrier
 // that is already complete, is a single inlined try_wait (about 17 cycles).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __noinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               unsigned long long limit_ns) {
     const unsigned long long t0 = global_ns();
     while (true) {
         for (int i = 0; i < 16; ++i)
             if (mbar_try_wait_sleep(bar, parity, 100000u)) return true;   // sleeps, up to 0.1 ms at a time
         if (*abort_flag) return false;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        if (global_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limited(bar, parity, abort_flag, WAIT_LIMIT_NS);
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -790,7 +794,34 @@ int launch_one(const GemmArgs& args, long long T, int slots, const float* w, con
     return INFMOE_OK;
 }
 
+// One warp waits on a barrier that nothing ever completes, through the same bounded wait the GEMM roles use, with
+// a caller-chosen limit: the way to see the expiry path (flag, status bit, orderly return) without a real stall.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* status, unsigned long long* waited_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const unsigned long long t0 = global_ns();
+    const bool done = mbar_wait_limited(smem_u32(&bar), 0, &s_abort, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!done && s_abort) atomicOr(status, STATUS_WAIT_TIMEOUT);
+        *waited_ns = global_ns() - t0;
+    }
+}
+
 }  // namespace
+
+int launch_wait_probe(unsigned long long limit_ns, int* status, unsigned long long* waited_ns, cudaStream_t stream) {
+    wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, status, waited_ns);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
 
 bool ffn_umma_supported(int D, int F, int E) {
     return D % 4 == 0 && F % 4 == 0 && D >= 8 && F >= 8 && E <= MAX_EXPERTS;

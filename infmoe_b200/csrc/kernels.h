@@ -41,6 +41,9 @@ int launch_ffn_simt(long long T, int D, int F, int e_begin, int e_end, const int
                     const float* h_hi, const float* h_lo, const float* w01, const float* wo, const float* routed,
                     float* g_hi, float* g_lo, float* post, cudaStream_t stream);
 
+// A one-warp kernel that waits, with the GEMM's bounded wait and the given limit, on a barrier nobody completes.
+int launch_wait_probe(unsigned long long limit_ns, int* status, unsigned long long* waited_ns, cudaStream_t stream);
+
 bool ffn_umma_supported(int D, int F, int E);
 // out_pos != NULL: `post` is the layer output in token order, row j of the experts' result goes to row out_pos[j]
 // (and mix_score != NULL applies the base_layer output mix on the way): the combine step fused into the epilogue.

@@ -738,6 +738,33 @@ std::vector<CachePlan> plan_cache(infmoe_layer* L, const std::vector<int>& activ
 
 }  // namespace
 
+int infmoe_wait_timeout_probe(uint32_t limit_ms, int32_t* timed_out, float* waited_ms) {
+    if (limit_ms == 0 || limit_ms > 2000 || !timed_out) {
+        set_error("wait_timeout_probe: the limit must be 1..2000 ms");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    int* d_status = nullptr;
+    unsigned long long* d_ns = nullptr;
+    INFMOE_CUDA_TRY(cudaMalloc(&d_status, sizeof(int)));
+    INFMOE_CUDA_TRY(cudaMalloc(&d_ns, sizeof(unsigned long long)));
+    int rc = INFMOE_OK, h_status = 0;
+    unsigned long long h_ns = 0;
+    if (cudaMemset(d_status, 0, sizeof(int)) != cudaSuccess) rc = INFMOE_ERR_CUDA;
+    if (rc == INFMOE_OK) rc = launch_wait_probe((unsigned long long)limit_ms * 1000000ull, d_status, d_ns, 0);
+    if (rc == INFMOE_OK && (cudaMemcpy(&h_status, d_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess ||
+                            cudaMemcpy(&h_ns, d_ns, sizeof(h_ns), cudaMemcpyDeviceToHost) != cudaSuccess)) {
+        set_error("wait_timeout_probe: %s", cudaGetErrorString(cudaGetLastError()));
+        rc = INFMOE_ERR_CUDA;
+    }
+    cudaFree(d_status);
+    cudaFree(d_ns);
+    if (rc != INFMOE_OK) return rc;
+    *timed_out = (h_status & STATUS_WAIT_TIMEOUT) ? 1 : 0;
+    if (waited_ms) *waited_ms = (float)(h_ns * 1e-6);
+    // the same translation enqueue's callers see
+    return *timed_out ? INFMOE_OK : status_to_rc(h_status);
+}
+
 int infmoe_expert_cache_simulate(int32_t slots, int32_t expert_count, const int32_t* experts, const int32_t* call_sizes,
                                  int32_t calls, int32_t* loads_per_call) {
     if (slots <= 0 || expert_count <= 0 || calls < 0 || (calls > 0 && (!experts || !call_sizes || !loads_per_call))) {

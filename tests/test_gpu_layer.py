@@ -166,6 +166,22 @@ def test_forward_host_into_page_locked_output(torch_cuda, oracle, variant):
     layer.terminate()
 
 
+def test_bounded_wait_runs_out_and_leaves_the_context_usable(torch_cuda, oracle, tmp_path):
+    """The wait every role of the expert GEMM uses, pointed at a barrier nothing completes, with a 50 ms limit:
+    it gives up, raises the status bit and returns; the next layer call on the same context works."""
+    import ctypes
+
+    from infmoe_b200 import capi, synth
+    timed_out, waited = ctypes.c_int32(0), ctypes.c_float(0)
+    capi.check(capi.lib().infmoe_wait_timeout_probe(50, ctypes.byref(timed_out), ctypes.byref(waited)))
+    assert timed_out.value == 1
+    assert 50.0 <= waited.value < 200.0
+    w = synth.scaled(synth.WORKLOADS["tiny_default"], variant="cpm_2")
+    layer, x, c, ln, experts = _build(w, synth, tmp_path)
+    _check(layer, w, x, c, ln, experts, oracle, torch_cuda)
+    layer.terminate()
+
+
 def test_exact_path_matches_tensor_core_path(torch_cuda, oracle, monkeypatch):
     from infmoe_b200 import synth
     w = synth.scaled(synth.WORKLOADS["base_layer_zipf"], expert_count=8, embedding_size=128, hidden_size=256, batch=2,
