@@ -76,23 +76,48 @@ __device__ __forceinline__ float4 load_row4(const float* __restrict__ row, int b
 __device__ __forceinline__ void warp_row_stats(const float* __restrict__ row, int D, bool vec, float& mean,
                                                float& rstd) {
     const int lane = threadIdx.x & 31;
+    // Same additions in the same order either way; the vector form (D a multiple of 4, aligned rows) has no
+    // per-element bounds checks and keeps eight loads in flight.
     float s = 0.f;
-    for (int base = 4 * lane; base < D; base += 128) {
-        const float4 v = load_row4(row, base, D, vec);
-        s = __fadd_rn(s, v.x);
-        if (base + 1 < D) s = __fadd_rn(s, v.y);
-        if (base + 2 < D) s = __fadd_rn(s, v.z);
-        if (base + 3 < D) s = __fadd_rn(s, v.w);
+    if (vec) {
+#pragma unroll 8
+        for (int base = 4 * lane; base < D; base += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(row + base);
+            s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, v.x), v.y), v.z), v.w);
+        }
+    } else {
+        for (int base = 4 * lane; base < D; base += 128) {
+            const float4 v = load_row4(row, base, D, false);
+            s = __fadd_rn(s, v.x);
+            if (base + 1 < D) s = __fadd_rn(s, v.y);
+            if (base + 2 < D) s = __fadd_rn(s, v.z);
+            if (base + 3 < D) s = __fadd_rn(s, v.w);
+        }
     }
     mean = __fdiv_rn(warp_xor_sum(s), (float)D);
     float q = 0.f;
-    for (int base = 4 * lane; base < D; base += 128) {
-        const float4 v = load_row4(row, base, D, vec);
-        float d = __fsub_rn(v.x, mean);
-        q = __fmaf_rn(d, d, q);
-        if (base + 1 < D) { d = __fsub_rn(v.y, mean); q = __fmaf_rn(d, d, q); }
-        if (base + 2 < D) { d = __fsub_rn(v.z, mean); q = __fmaf_rn(d, d, q); }
-        if (base + 3 < D) { d = __fsub_rn(v.w, mean); q = __fmaf_rn(d, d, q); }
+    if (vec) {
+#pragma unroll 8
+        for (int base = 4 * lane; base < D; base += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(row + base);
+            float d = __fsub_rn(v.x, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v.y, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v.z, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v.w, mean);
+            q = __fmaf_rn(d, d, q);
+        }
+    } else {
+        for (int base = 4 * lane; base < D; base += 128) {
+            const float4 v = load_row4(row, base, D, false);
+            float d = __fsub_rn(v.x, mean);
+            q = __fmaf_rn(d, d, q);
+            if (base + 1 < D) { d = __fsub_rn(v.y, mean); q = __fmaf_rn(d, d, q); }
+            if (base + 2 < D) { d = __fsub_rn(v.z, mean); q = __fmaf_rn(d, d, q); }
+            if (base + 3 < D) { d = __fsub_rn(v.w, mean); q = __fmaf_rn(d, d, q); }
+        }
     }
     const float var = __fdiv_rn(warp_xor_sum(q), (float)D);
     rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-6f)));
