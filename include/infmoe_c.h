@@ -130,6 +130,17 @@ INFMOE_API int infmoe_layer_expert_forward(infmoe_layer* layer, const float* d_r
                                            float* d_y, void* d_workspace, size_t workspace_bytes, int64_t rows,
                                            void* stream);
 
+/* infmoe_layer_expert_forward with the combine step of the expert-parallel path folded in: the result of row i is
+ * written to the address d_row_dst[i] (embedding_size floats), which may lie in another GPU's memory that this
+ * process has mapped (peer access / CUDA IPC) -- the owner of the experts stores each row straight into the output
+ * buffer of the rank the token came from, instead of returning rows for a second all-to-all.  d_row_score (or NULL):
+ * the routing scores of the rows; with the base_layer variant they switch on its output mix
+ * (plugin/cuda/moe.cu:115-127), which then also happens here.  No counterpart in the reference (single GPU). */
+INFMOE_API int infmoe_layer_expert_forward_scatter(infmoe_layer* layer, const float* d_rows,
+                                                   const int32_t* d_expert_of_row, const float* d_row_score,
+                                                   const uint64_t* d_row_dst, void* d_workspace,
+                                                   size_t workspace_bytes, int64_t rows, void* stream);
+
 /* Blocks until `stream` is idle and returns the device-side status of the calls enqueued so far. */
 INFMOE_API int infmoe_layer_sync_status(infmoe_layer* layer, void* stream);
 

@@ -66,6 +66,7 @@ SIGNATURES = {
     "infmoe_layer_workspace_bytes": [_vp, _i64, ctypes.POINTER(_sz)],
     "infmoe_layer_enqueue": [_vp, _vp, _vp, _vp, _sz, _i64, _vp],
     "infmoe_layer_expert_forward": [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _vp],
+    "infmoe_layer_expert_forward_scatter": [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _vp],
     "infmoe_layer_sync_status": [_vp, _vp],
     "infmoe_layer_forward_host": [_vp, _vp, _vp, _i64],
     "infmoe_layer_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,

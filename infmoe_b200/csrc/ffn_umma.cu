@@ -277,6 +277,8 @@ struct GemmArgs {
     const int* out_pos;         // RESIDUAL: row j is written to row out_pos[j] of y (NULL: row j), i.e. the combine
                                 // step moe_expert_gather (plugin/cuda/moe.cu:89-96) fused into the epilogue
     const float* mix_score;     // RESIDUAL: routed scores for the base_layer output mix (NULL: no mix)
+    const unsigned long long* out_row_ptr;   // RESIDUAL: address of output row i (i = out_pos[j] or j) instead of
+                                             // y + i * M_total; the rows may live in another GPU's memory
     int* status;
 };
 
@@ -563,17 +565,22 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 // (lanes 16..31 repeat them), handed out by shuffle below
                 int lane_row = 0;
                 float lane_alpha = 0.f;
+                unsigned long long lane_ptr = 0;
                 if (EPI == EPI_RESIDUAL) {
                     const int lc = sl * 16 + (lane & 15);
                     const int r = t.row0 + lc;
                     lane_row = (lc < t.n_tok && args.out_pos) ? args.out_pos[r] : r;
                     if (args.mix_score && lc < t.n_tok) lane_alpha = mix_alpha(args.mix_score[r]);
+                    if (lc < t.n_tok)
+                        lane_ptr = args.out_row_ptr
+                                       ? args.out_row_ptr[lane_row]
+                                       : (unsigned long long)(args.out_hi + (size_t)lane_row * (size_t)args.M_total);
                 }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const int col = sl * 16 + c;
                     const float v = sum[i][c];
-                    const int out_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_row, c) : 0;
+                    const unsigned long long out_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_ptr, c) : 0ull;
                     const float alpha = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_alpha, c) : 0.f;
                     if (EPI == EPI_GELU_PAIR) {
                         // even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index
@@ -602,7 +609,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             const float x = args.resid[o];
                             float y = __fadd_rn(x, v);
                             if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
-                            args.out_hi[(size_t)out_row * (size_t)args.M_total + (size_t)m] = y;
+                            reinterpret_cast<float*>(out_row)[m] = y;
                         }
                     }
                 }
@@ -836,7 +843,7 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
                     const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
                     const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
                     int num_sms, cudaStream_t stream, cudaEvent_t mid_event, const int* out_pos,
-                    const float* mix_score) {
+                    const float* mix_score, const unsigned long long* out_row_ptr) {
     if (T == 0 || e_begin >= e_end) return INFMOE_OK;
     if (!ffn_umma_supported(D, F, E)) {
         set_error("ffn_umma: unsupported shape D=%d F=%d E=%d", D, F, E);
@@ -862,6 +869,7 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
     a2.resid = routed;
     a2.out_pos = out_pos;
     a2.mix_score = mix_score;
+    a2.out_row_ptr = out_row_ptr;
     // Shapes: token chunk, weight stages (16 KB each), token stages.  INFMOE_GEMM_TILE selects another instantiation
     // for tuning runs.
     static const int variant = [] {

@@ -47,10 +47,13 @@ int launch_wait_probe(unsigned long long limit_ns, int* status, unsigned long lo
 bool ffn_umma_supported(int D, int F, int E);
 // out_pos != NULL: `post` is the layer output in token order, row j of the experts' result goes to row out_pos[j]
 // (and mix_score != NULL applies the base_layer output mix on the way): the combine step fused into the epilogue.
+// out_row_ptr != NULL: row out_pos[j] is written to the address out_row_ptr[out_pos[j]] instead.
 int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, const int* offset,
                     const int* slot_of_expert, int slots, const float* h_hi, const float* h_lo, const float* w01,
                     const float* wo, const float* routed, float* g_hi, float* g_lo, float* post, int* status,
                     int num_sms, cudaStream_t stream, cudaEvent_t mid_event = nullptr, const int* out_pos = nullptr,
-                    const float* mix_score = nullptr);
+                    const float* mix_score = nullptr, const unsigned long long* out_row_ptr = nullptr);
+// Rows of `in` [n][D] copied to the addresses dst[i] (one per row; they may point into a peer GPU's memory).
+int launch_rows_to_ptrs(long long n, int D, const float* in, const unsigned long long* dst, cudaStream_t stream);
 
 }  // namespace infmoe

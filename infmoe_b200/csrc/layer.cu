@@ -357,6 +357,7 @@ struct FfnOutput {
     float* out = nullptr;
     const int* pos = nullptr;
     const float* mix_score = nullptr;
+    const unsigned long long* row_ptr = nullptr;   // address of output row i instead of out + i * D
 };
 
 bool uses_umma(const infmoe_layer* L) { return L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E); }
@@ -367,7 +368,7 @@ int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_o
     if (uses_umma(L))
         return launch_ffn_umma(T, L->D, L->F, L->E, e_begin, e_end, d_offset, d_slot_map, slots, h_hi, h_lo, planes[0],
                                planes[1], routed, g_hi, g_lo, o.out ? o.out : o.post, L->d_status, L->num_sms, stream,
-                               mid, o.out ? o.pos : nullptr, o.out ? o.mix_score : nullptr);
+                               mid, o.out ? o.pos : nullptr, o.out ? o.mix_score : nullptr, o.out ? o.row_ptr : nullptr);
     float* post = o.post;
     return launch_ffn_simt(T, L->D, L->F, e_begin, e_end, d_offset, d_slot_map, h_hi, h_lo, planes[0], planes[1],
                            routed, g_hi, g_lo, post, stream);
@@ -812,8 +813,9 @@ int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes
 // output in the caller's row order (no score mix): the building block of the expert-parallel path, where
 // routing happened on the rank that owns the token.
 static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
-                     void* stream_v, const int* given_gate) {
-    if (!L || T < 0 || (T > 0 && (!d_in || !d_out || !d_ws))) {
+                     void* stream_v, const int* given_gate, const float* row_score = nullptr,
+                     const unsigned long long* row_dst = nullptr) {
+    if (!L || T < 0 || (T > 0 && (!d_in || (!d_out && !row_dst) || !d_ws))) {
         set_error("layer_enqueue: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
@@ -864,7 +866,7 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     float* g_hi = (float*)(base + w.g_hi);
     float* g_lo = (float*)(base + w.g_lo);
     const int* gate_in = given_gate ? given_gate : gate;
-    if (given_gate) score = nullptr;
+    if (given_gate) score = const_cast<float*>(row_score);   // scores of the caller's rows, or none
     L->last_gate = gate_in;
     L->last_score = score;
     L->last_pos = pos;
@@ -880,15 +882,16 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     // 2. dispatch metadata (:350-352)
     INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 2, stream));
-    const bool mix = L->flags.base_layer_mix && !given_gate;
+    const bool mix = L->flags.base_layer_mix && (!given_gate || row_score);
     // the tensor-core GEMM writes the layer output itself (combine fused into its epilogue)
     const bool fused_combine = !L->identity && uses_umma(L);
     FfnOutput ffn_out;
     ffn_out.post = post;
     if (fused_combine) {
-        ffn_out.out = d_out;
+        ffn_out.out = row_dst ? post : d_out;   // with per-row addresses `out` only switches the fused path on
         ffn_out.pos = pos;
         ffn_out.mix_score = mix ? rscore : nullptr;
+        ffn_out.row_ptr = row_dst;
     }
     if (L->identity) {
         // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
@@ -989,10 +992,16 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     INFMOE_TRY(prof_mark(L, 5, stream));
     // 5. combine (:407-412; the gather reads the expert output), unless the GEMM epilogue has done it
     if (fused_combine) {
-    } else if (mix)
-        INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, d_out, stream));
-    else
-        INFMOE_TRY(launch_gather(T, L->D, post, pos, d_out, stream));
+    } else {
+        // with per-row addresses the rows are first combined in the caller's row order (g_hi is free by now:
+        // T x d_ff floats), then copied out
+        float* ordered = row_dst ? g_hi : d_out;
+        if (mix)
+            INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, ordered, stream));
+        else
+            INFMOE_TRY(launch_gather(T, L->D, post, pos, ordered, stream));
+        if (row_dst) INFMOE_TRY(launch_rows_to_ptrs(T, L->D, ordered, row_dst, stream));
+    }
     INFMOE_TRY(prof_mark(L, 6, stream));
     if (L->profiling) L->prof_calls++;
     return INFMOE_OK;
@@ -1011,6 +1020,22 @@ int infmoe_layer_expert_forward(infmoe_layer* L, const float* d_rows, const int3
     }
     if (rows == 0) return INFMOE_OK;
     return layer_run(L, d_rows, d_out, d_ws, ws_bytes, rows, stream_v, d_expert_of_row);
+}
+
+int infmoe_layer_expert_forward_scatter(infmoe_layer* L, const float* d_rows, const int32_t* d_expert_of_row,
+                                        const float* d_row_score, const uint64_t* d_row_dst, void* d_ws,
+                                        size_t ws_bytes, int64_t rows, void* stream_v) {
+    if (rows > 0 && (!d_expert_of_row || !d_row_dst)) {
+        set_error("layer_expert_forward_scatter: expert index and destination arrays are required");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0) return INFMOE_OK;
+    if (L && L->F < L->D) {
+        set_error("layer_expert_forward_scatter: needs d_ff >= d_model");   // the ordered rows borrow a d_ff-wide plane
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    return layer_run(L, d_rows, nullptr, d_ws, ws_bytes, rows, stream_v, d_expert_of_row, d_row_score,
+                     reinterpret_cast<const unsigned long long*>(d_row_dst));
 }
 
 int infmoe_layer_sync_status(infmoe_layer* L, void* stream_v) {

@@ -262,6 +262,36 @@ int launch_scatter_ln_split(long long T, int D, const float* X, const float* sco
     return INFMOE_OK;
 }
 
+namespace {
+// in[i,:] -> the row at address dst[i]
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rows_to_ptrs_kernel(long long n, int D, int vec, const float* __restrict__ in, const unsigned long long* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (j >= n) return;
+    const float* a = in + j * D;
+    float* o = reinterpret_cast<float*>(dst[j]);
+    if (vec && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+        for (int i = lane; i < D / 4; i += 32) reinterpret_cast<float4*>(o)[i] = reinterpret_cast<const float4*>(a)[i];
+    } else {
+        for (int i = lane; i < D; i += 32) o[i] = a[i];
+    }
+}
+}  // namespace
+
+int launch_rows_to_ptrs(long long n, int D, const float* in, const unsigned long long* dst, cudaStream_t stream) {
+    if (n < 0 || D <= 0 || !in || !dst) {
+        set_error("rows_to_ptrs: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (n == 0) return INFMOE_OK;
+    const int vec = (D % 4 == 0) && aligned16(in);
+    rows_to_ptrs_kernel<<<row_grid(n), ROW_WARPS * 32, 0, stream>>>(n, D, vec, in, dst);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
 int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream) {
     if (T < 0 || D <= 0 || !in || !pos || !out) {
         set_error("expert_gather: bad argument");

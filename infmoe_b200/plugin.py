@@ -158,6 +158,21 @@ class MoELayer:
                                                           out.data_ptr(), self._ws.data_ptr(), self._ws.numel(), n, s))
         return out
 
+    def expert_forward_scatter(self, rows, expert_of_row, row_dst, row_score=None, stream: Optional[int] = None):
+        """Experts on `rows`; the result of row i goes to the address row_dst[i] (int64/uint64 CUDA tensor)."""
+        import torch
+
+        n = rows.shape[0]
+        if n == 0:
+            return
+        need = self.get_workspace_size(n)
+        if self._ws is None or self._ws.numel() < need or self._ws.device != rows.device:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=rows.device)
+        s = torch.cuda.current_stream(rows.device).cuda_stream if stream is None else stream
+        capi.check(capi.lib().infmoe_layer_expert_forward_scatter(
+            self._h, rows.data_ptr(), expert_of_row.data_ptr(), row_score.data_ptr() if row_score is not None else None,
+            row_dst.data_ptr(), self._ws.data_ptr(), self._ws.numel(), n, s))
+
     def sync_status(self, stream: int = 0) -> None:
         capi.check(capi.lib().infmoe_layer_sync_status(self._h, stream))
 

@@ -182,6 +182,40 @@ def test_bounded_wait_runs_out_and_leaves_the_context_usable(torch_cuda, oracle,
     layer.terminate()
 
 
+@pytest.mark.parametrize("variant,path", [("cpm_2", ""), ("base_layer", ""), ("base_layer", "simt")])
+def test_expert_forward_scatter_writes_rows_to_given_addresses(torch_cuda, oracle, monkeypatch, variant, path):
+    """The expert-parallel building block: rows with known experts, each result written to its own address
+    (here: a permutation of the rows of a local tensor), optionally with the base_layer mix."""
+    from infmoe_b200 import synth
+    torch = torch_cuda
+    if path:
+        monkeypatch.setenv("INFMOE_FFN", path)
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=6, embedding_size=128, hidden_size=256,
+                     batch=1, seq_len=300)
+    layer, x, c, ln, experts = _build(w, synth, from_npz=False)
+    rng = np.random.default_rng(5)
+    n, D = w.tokens, w.embedding_size
+    expert_of_row = torch.from_numpy(rng.integers(0, w.expert_count, n).astype(np.int32)).cuda()
+    rows = torch.from_numpy(x).cuda()
+    want = layer.expert_forward(rows, expert_of_row)            # rows in, rows out, same order
+    perm = torch.from_numpy(rng.permutation(n)).cuda()
+    out = torch.full((n, D), float("nan"), device="cuda")
+    dst = out.data_ptr() + perm.to(torch.int64) * (D * 4)
+    score = None
+    if variant == "base_layer":
+        score = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+        alpha = torch.sigmoid(score.double())[:, None]
+        want = (alpha * want.double() + (1 - alpha) * rows.double()).float()
+    layer.expert_forward_scatter(rows, expert_of_row, dst.contiguous(), score)
+    layer.sync_status()
+    got = out[perm]
+    if variant == "base_layer":
+        torch.testing.assert_close(got, want, rtol=2e-6, atol=2e-6)
+    else:
+        assert torch.equal(got, want)
+    layer.terminate()
+
+
 def test_exact_path_matches_tensor_core_path(torch_cuda, oracle, monkeypatch):
     from infmoe_b200 import synth
     w = synth.scaled(synth.WORKLOADS["base_layer_zipf"], expert_count=8, embedding_size=128, hidden_size=256, batch=2,
