@@ -134,8 +134,9 @@ INFMOE_API int infmoe_layer_expert_forward(infmoe_layer* layer, const float* d_r
  * written to the address d_row_dst[i] (embedding_size floats), which may lie in another GPU's memory that this
  * process has mapped (peer access / CUDA IPC) -- the owner of the experts stores each row straight into the output
  * buffer of the rank the token came from, instead of returning rows for a second all-to-all.  d_row_score (or NULL):
- * the routing scores of the rows; with the base_layer variant they switch on its output mix
- * (plugin/cuda/moe.cu:115-127), which then also happens here.  No counterpart in the reference (single GPU). */
+ * the routing scores of the rows; passing them asks for the base_layer output mix
+ * out = sigmoid(score) * expert(row) + (1 - sigmoid(score)) * row (plugin/cuda/moe.cu:115-127), whatever the
+ * variant this layer object was created with.  No counterpart in the reference (single GPU). */
 INFMOE_API int infmoe_layer_expert_forward_scatter(infmoe_layer* layer, const float* d_rows,
                                                    const int32_t* d_expert_of_row, const float* d_row_score,
                                                    const uint64_t* d_row_dst, void* d_workspace,

@@ -882,7 +882,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     // 2. dispatch metadata (:350-352)
     INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 2, stream));
-    const bool mix = L->flags.base_layer_mix && (!given_gate || row_score);
+    // whole layer: the variant decides; experts alone: the caller asks for the mix by passing the scores
+    const bool mix = given_gate ? row_score != nullptr : L->flags.base_layer_mix;
     // the tensor-core GEMM writes the layer output itself (combine fused into its epilogue)
     const bool fused_combine = !L->identity && uses_umma(L);
     FfnOutput ffn_out;

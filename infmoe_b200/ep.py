@@ -81,6 +81,9 @@ class CudaStages:
     def experts(self, rows, expert_of_row):
         return self.layer.expert_forward(rows, expert_of_row)
 
+    def experts_to(self, rows, expert_of_row, row_dst, row_score=None):
+        self.layer.expert_forward_scatter(rows, expert_of_row, row_dst, row_score)
+
     def combine(self, post, routed, rscore, pos):
         T, D = post.shape
         out = torch.empty_like(post)
@@ -100,12 +103,73 @@ class CudaStages:
         self.layer.sync_status(self._stream())
 
 
+class PeerOutput:
+    """The output buffer of every rank, mapped into this process (CUDA IPC over NVLink peer access).
+
+    Each rank allocates [rows][D] floats with cudaMalloc (an IPC handle needs the base of an allocation, which a
+    block of the caching allocator is not), publishes the handle, and opens the handles of the others.  `base[r]`
+    is the address of rank r's buffer as seen from here; `tensor` is this rank's own buffer.
+    """
+
+    def __init__(self, rows: int, D: int, group=None):
+        from cuda.bindings import runtime as rt
+        self._rt = rt
+        self.rows, self.D = rows, D
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        err, ptr = rt.cudaMalloc(max(rows, 1) * D * 4)
+        self._check(err, "cudaMalloc")
+        self._own = int(ptr)
+        err, handle = rt.cudaIpcGetMemHandle(self._own)
+        self._check(err, "cudaIpcGetMemHandle")
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.reserved), group=group)
+        self.base, self._opened = [], []
+        for r, raw in enumerate(handles):
+            if r == rank:
+                self.base.append(self._own)
+                continue
+            h = rt.cudaIpcMemHandle_t()
+            h.reserved = raw
+            err, p = rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess)
+            self._check(err, f"cudaIpcOpenMemHandle (rank {r})")
+            self.base.append(int(p))
+            self._opened.append(int(p))
+
+        class _View:   # minimal CUDA array interface over the raw allocation
+            __cuda_array_interface__ = {"shape": (max(rows, 1), D), "typestr": "<f4", "data": (self._own, False),
+                                        "version": 2}
+
+        self.tensor = torch.as_tensor(_View(), device=torch.device("cuda", torch.cuda.current_device()))[:rows]
+        self.base_dev = torch.tensor(self.base, dtype=torch.int64, device=self.tensor.device)
+
+    @staticmethod
+    def _check(err, what):
+        if int(err) != 0:
+            raise RuntimeError(f"{what} failed with CUDA error {int(err)}")
+
+    def close(self):
+        """Every rank must have finished writing (a barrier) before anybody calls this."""
+        rt = self._rt
+        for p in self._opened:
+            rt.cudaIpcCloseMemHandle(p)
+        self._opened = []
+        if self._own:
+            self.tensor = None
+            rt.cudaFree(self._own)
+            self._own = 0
+
+
 class ExpertParallelMoE:
     """forward(x_local) -> out_local for one MoE layer sharded over the ranks of `group`."""
 
-    def __init__(self, stages, expert_count: int, group=None):
+    def __init__(self, stages, expert_count: int, group=None, peer_output: bool = False):
+        """peer_output: the owner of an expert writes each result row straight into the output buffer of the rank
+        the token came from (peer stores from the GEMM epilogue) instead of sending rows back through a second
+        all-to-all; needs CUDA ranks with peer access and stages that offer `experts_to`."""
         self.stages = stages
         self.group = group
+        self.peer_output = peer_output
+        self._peer = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.expert_count = expert_count
@@ -122,6 +186,13 @@ class ExpertParallelMoE:
 
     PHASES = ("local_route_dispatch_scatter", "counts_exchange", "rows_out", "experts", "rows_back", "combine")
 
+    def close(self):
+        if self._peer is not None:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self._peer.close()
+            self._peer = None
+
     def set_timing(self, enable: bool) -> None:
         """Record CUDA events between the phases of forward(); read them with phase_ms()."""
         self._timing = [] if enable else None
@@ -137,6 +208,33 @@ class ExpertParallelMoE:
             for i in range(len(self.PHASES)):
                 tot[i] += ev[i].elapsed_time(ev[i + 1])
         return {name: t / len(calls) for name, t in zip(self.PHASES, tot)}
+
+    def _experts_to_peers(self, x, received, expert_of_row, pos, rscore, send_rows, recv_rows, mark):
+        """The return path without a second row exchange: the token index of every row (and, for the base_layer
+        mix, its score) travels with it; the owner turns them into addresses inside the source rank's output
+        buffer and the GEMM epilogue stores the rows there; one small collective orders the stores before the
+        buffers are read."""
+        T, D = x.shape
+        if self._peer is None or self._peer.rows != T or self._peer.D != D:
+            if self._peer is not None:
+                self.close()
+            self._peer = PeerOutput(T, D, self.group)
+        peer = self._peer
+        home = self._all_to_all(pos.to(torch.int32).contiguous(), recv_rows, send_rows)   # token index at the source
+        src = torch.repeat_interleave(torch.arange(self.world), torch.tensor(recv_rows)).to(x.device, non_blocking=True)
+        dst = peer.base_dev[src] + home.to(torch.int64) * (D * 4)
+        scores = None
+        if self.stages.variant == "base_layer":
+            scores = self._all_to_all(rscore.contiguous(), recv_rows, send_rows)
+        self.stages.experts_to(received, expert_of_row, dst.contiguous(), scores)
+        mark()
+        # every rank's stores are complete, and visible, before any rank reads its buffer
+        flag = torch.zeros(1, device=x.device)
+        dist.all_reduce(flag, group=self.group)
+        mark()
+        out = peer.tensor.clone()
+        mark()
+        return out
 
     def forward(self, x):
         R, E = self.world, self.expert_count
@@ -173,12 +271,16 @@ class ExpertParallelMoE:
         local_ids = torch.arange(per, dtype=torch.int32).repeat(R)
         expert_of_row = torch.repeat_interleave(local_ids, recv_mat.reshape(-1).to(torch.int64)).to(
             x.device, non_blocking=True)
-        processed = self.stages.experts(received, expert_of_row.contiguous())
-        mark()
-        post = self._all_to_all(processed, send_rows, recv_rows)
-        mark()
-        out = self.stages.combine(post, routed, rscore, pos)
-        mark()
+        if self.peer_output and R > 1:
+            out = self._experts_to_peers(x, received, expert_of_row.contiguous(), pos, rscore, send_rows, recv_rows,
+                                         mark)
+        else:
+            processed = self.stages.experts(received, expert_of_row.contiguous())
+            mark()
+            post = self._all_to_all(processed, send_rows, recv_rows)
+            mark()
+            out = self.stages.combine(post, routed, rscore, pos)
+            mark()
         if marks:
             self._timing.append(marks)
         self.last = {"gate": gate, "score": score, "pos": pos, "count": count, "recv_counts": recv_mat}

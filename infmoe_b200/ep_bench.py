@@ -41,7 +41,9 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
     for e in range(lo, hi):
         local.set_expert(e - lo, *synth.gen_expert_torch(total, e, dev))
     local.set_residency(1)
-    moe = ExpertParallelMoE(CudaStages(local, cent, ln, total.variant), E)
+    # INFMOE_EP_PEER_OUTPUT=0: return the rows through a second all-to-all instead of peer stores from the GEMM epilogue
+    peer_output = os.environ.get("INFMOE_EP_PEER_OUTPUT", "1") != "0" and world > 1
+    moe = ExpertParallelMoE(CudaStages(local, cent, ln, total.variant), E, peer_output=peer_output)
 
     hx = torch.from_numpy(x_local).pin_memory()
     hout = torch.empty_like(hx).pin_memory()
@@ -110,7 +112,9 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
         T_total = T_local * world
         cfg = workload_config(total, world)
         cfg.update({"parallelism": f"ep{world}", "tokens_per_gpu": T_local, "experts_per_gpu": hi - lo,
-                    "exchange": "NCCL all_to_all_single (counts, rows out, rows back)"})
+                    "exchange": ("NCCL all_to_all_single (counts, rows out); results stored by the owner's GEMM epilogue into the "
+                                 "source rank's output buffer (CUDA IPC peer memory)") if peer_output
+                    else "NCCL all_to_all_single (counts, rows out, rows back)"})
         line = {
             "metric": metric, "value": T_total / (float(ms.item()) * 1e-3), "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms.item()),
@@ -124,6 +128,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
             "roofline": roofline, "cpu_baseline": None, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
+    moe.close()
     local.terminate()
     dist.barrier()
     dist.destroy_process_group()

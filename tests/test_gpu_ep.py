@@ -20,7 +20,7 @@ def _workload(variant):
                         batch=2, seq_len=333)
 
 
-def _worker(rank, world, port, variant, ret):
+def _worker(rank, world, port, variant, peer_output, ret):
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -35,7 +35,7 @@ def _worker(rank, world, port, variant, ret):
         local = MoELayer.create(hi - lo, w.embedding_size, w.hidden_size, 2, c[lo:hi], None, "T5_FF", "default", None)
         for e in range(lo, hi):
             local.set_expert(e - lo, *synth.gen_expert_numpy(w, e))
-        moe = ExpertParallelMoE(CudaStages(local, c, ln, variant), w.expert_count)
+        moe = ExpertParallelMoE(CudaStages(local, c, ln, variant), w.expert_count, peer_output=peer_output)
         per = w.tokens // world
         out = moe.forward(torch.from_numpy(x[rank * per:(rank + 1) * per].copy()).cuda())
         moe.stages.check()
@@ -43,14 +43,16 @@ def _worker(rank, world, port, variant, ret):
         torch.cuda.synchronize()
         assert torch.equal(out, out2)
         ret[rank] = dict(out=out.cpu().numpy(), gate=moe.last["gate"].cpu().numpy())
+        moe.close()
         local.terminate()
         dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("peer_output", [False, True])
 @pytest.mark.parametrize("variant", ["cpm_2", "base_layer"])
-def test_two_gpus_match_single_gpu_and_oracle(oracle, variant):
+def test_two_gpus_match_single_gpu_and_oracle(oracle, variant, peer_output):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -58,7 +60,7 @@ def test_two_gpus_match_single_gpu_and_oracle(oracle, variant):
     world = 2
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), variant, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), variant, peer_output, ret), nprocs=world, join=True)
         res = [ret[r] for r in range(world)]
     from infmoe_b200 import MoELayer, synth
     w = _workload(variant)
