@@ -41,8 +41,10 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
     for e in range(lo, hi):
         local.set_expert(e - lo, *synth.gen_expert_torch(total, e, dev))
     local.set_residency(1)
-    # INFMOE_EP_PEER_OUTPUT=0: return the rows through a second all-to-all instead of peer stores from the GEMM epilogue
-    peer_output = os.environ.get("INFMOE_EP_PEER_OUTPUT", "1") != "0" and world > 1
+    # Return path: peer stores from the GEMM epilogue (INFMOE_EP_PEER_OUTPUT=1) or a second all-to-all (=0).  The
+    # default is the peer path on 2 GPUs, where it has been run and checked bit for bit; larger worlds keep the
+    # all-to-all until the peer path has been run there too.
+    peer_output = os.environ.get("INFMOE_EP_PEER_OUTPUT", "1" if world == 2 else "0") != "0" and world > 1
     moe = ExpertParallelMoE(CudaStages(local, cent, ln, total.variant), E, peer_output=peer_output)
 
     hx = torch.from_numpy(x_local).pin_memory()
