@@ -37,9 +37,12 @@ sys.path.insert(0, ROOT)
 
 from infmoe_b200 import synth  # noqa: E402
 
-# DRAM bytes the wi_0/wi_1 GEMM moves per weight element (ncu capture summarised under profiles/; 4 = each raw
-# FP32 weight crosses HBM once)
+# DRAM bytes the wi_0/wi_1 GEMM moves per weight element: dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture of workload cpm2_profile (profiles/ffn_umma_kernel_cpm2_profile.md) divided by the weight elements that
+# launch streams; 4 = each raw FP32 weight crosses HBM once.  It is a figure from that capture, scaled by the
+# elements this launch streams -- it is not measured by this run.
 TRAFFIC_BYTES_PER_WEIGHT = 4.28
+TRAFFIC_SOURCE = "ncu capture of cpm2_profile (profiles/ffn_umma_kernel_cpm2_profile.md), bytes per weight element x elements streamed"
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
@@ -230,6 +233,63 @@ def ref_gpu_baseline(w, torch, sample_experts=8, reps=3):
     return res
 
 
+def gemm_roofline(kernel, achieved_tflops, kernel_ms, peaks, clock_summary, timed_s):
+    """Roofline object of the grouped expert GEMM.
+
+    `peak` is what plain 3xTF32 (three TF32 MMAs per product) could reach: measured bf16 / 6.  The burst figure is
+    the denominator while the timed region is short and the SM clock sampled during it stays near its maximum; a
+    long region that runs into the power cap is held against the sustained figure.  `frac_own_mix` is against the
+    ceiling of the MMAs this kernel actually issues (one TF32 and two half-cost BF16 MMAs per product): bf16 / 4."""
+    sm, mx = clock_summary.get("sm_mhz"), clock_summary.get("sm_max_mhz")
+    burst = timed_s < 1.0 and sm is not None and mx and sm >= 0.9 * mx
+    bf16 = peaks["bf16_tflops"] if burst else peaks["bf16_sustained"]
+    regime = "burst" if burst else "sustained"
+    return {"kernel": kernel, "bound": "tensor", "achieved": achieved_tflops, "peak": bf16 / 6.0, "unit": "TFLOP/s",
+            "frac": achieved_tflops / (bf16 / 6.0), "frac_own_mix": achieved_tflops / (bf16 / 4.0),
+            "peak_source": f"bf16 {regime} {bf16} TFLOP/s of {peaks['source']} / 6 (TF32 = bf16 / 2, three MMAs per "
+                           f"product); own mix = 1 TF32 + 2 BF16 K=16 MMAs per product -> bf16 / 4; regime chosen from "
+                           f"the timed region ({timed_s:.2f} s) and the sampled SM clock ({sm} of {mx} MHz)",
+            "ms": kernel_ms}
+
+
+def routing_differences(w, x, cent, ln, gate, torch):
+    """How many tokens of this workload the fused FP32 routing sends elsewhere than (a) an FP64 evaluation and (b)
+    FP32 in cuBLAS's summation order followed by the reference's own select kernel (oracle/_ref, when it was
+    built), with the largest top-1/top-2 score margin (FP64) among those tokens: the distance between the
+    canonical summation order and the reference's, which only shows at near-ties."""
+    import ctypes
+    from oracle import oracle
+    gamma = ln if w.variant == "cpm_2" else None
+    g64, top1, top2 = oracle.route_f64(x, cent, gamma)
+    margin = top1 - top2
+    d64 = np.nonzero(g64 != gate)[0]
+    res = {"tokens": int(gate.size), "fp64_flips": int(d64.size),
+           "fp64_max_margin": float(margin[d64].max()) if d64.size else 0.0,
+           "score_std": float(np.std(top1))}
+    path = os.path.join(ROOT, "oracle", "_ref", "libinfmoe_ref_kernels.so")
+    if os.path.exists(path):
+        ref = ctypes.CDLL(path)
+        T, D, E = x.shape[0], x.shape[1], cent.shape[0]
+        dev = torch.device("cuda")
+        dx, dc = torch.from_numpy(x).to(dev), torch.from_numpy(cent).to(dev)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        if gamma is not None:
+            dn = torch.empty_like(dx)
+            assert ref.ref_layernorm(p(dn), p(dx), T, D, p(torch.from_numpy(gamma).to(dev))) == 0
+            dx = dn
+        aff = torch.empty(T, E, dtype=torch.float32, device=dev)
+        assert ref.ref_gating_sgemm(T, D, E, p(dc), p(dx), p(aff)) == 0
+        rg = torch.empty(T, dtype=torch.int32, device=dev)
+        rw = torch.empty(T, dtype=torch.float32, device=dev)
+        assert ref.ref_select(T, E, p(aff), p(rg), p(rw)) == 0
+        torch.cuda.synchronize()
+        dref = np.nonzero(rg.cpu().numpy() != gate)[0]
+        res.update({"reference_order_flips": int(dref.size),
+                    "reference_order_max_margin": float(margin[dref].max()) if dref.size else 0.0,
+                    "reference_order": "layernorm_gpu + cublasSgemm_v2 + expert_select_top1_kernel (oracle/_ref)"})
+    return res
+
+
 def run_single(args, w):
     import torch
 
@@ -282,20 +342,17 @@ def run_single(args, w):
     active = int(np.count_nonzero(np.bincount(gate, minlength=E)))
     g1_ms = stage_ms["ffn_gemm1"] if stage_ms["ffn_gemm1"] > 0 else None
     useful_flops = 4.0 * T * D * F                    # algorithmic flops of h wi_0^T and h wi_1^T
-    peak_3xtf32 = peaks["bf16_sustained"] / 6.0       # TF32 = bf16 / 2, three MMAs per product
+    clock_summary = clocks.summary()
     roofline = None
     if g1_ms:
         achieved = useful_flops / (g1_ms * 1e-3) / 1e12
         weight_bytes = (2 * D * F * 4.0) * active      # raw FP32 interleaved wi_0/wi_1 matrix of every active expert
-        # DRAM bytes per launch from the ncu capture of workload cpm2_profile (profiles/), expressed per weight
-        # element (4 algorithmic) and scaled by the weight elements this launch streams.
         traffic = TRAFFIC_BYTES_PER_WEIGHT * active * 2.0 * F * D if not w.streamed else None
-        roofline = {"kernel": "ffn_umma_kernel<EPI_GELU_PAIR>", "bound": "tensor", "achieved": achieved,
-                    "peak": peak_3xtf32, "unit": "TFLOP/s", "frac": achieved / peak_3xtf32, "traffic": traffic,
-                    "peak_source": f"bf16 sustained {peaks['bf16_sustained']} TFLOP/s of {peaks['source']} / 6 "
-                                   "(TF32 = bf16/2, 3 MMAs per product)",
-                    "ms": g1_ms, "weight_stream_gbs": weight_bytes / (g1_ms * 1e-3) / 1e9,
-                    "hbm_peak_gbs": peaks["hbm_gbs"]}
+        roofline = gemm_roofline("ffn_umma_kernel<EPI_GELU_PAIR>", achieved, g1_ms, peaks, clock_summary,
+                                 timed_s=ms * 1e-3 * args.steps)
+        roofline.update({"traffic": traffic, "traffic_source": TRAFFIC_SOURCE if traffic else None,
+                         "algorithmic_bytes": weight_bytes, "weight_stream_gbs": weight_bytes / (g1_ms * 1e-3) / 1e9,
+                         "hbm_peak_gbs": peaks["hbm_gbs"], "hbm_frac": weight_bytes / (g1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
 
     # ---- CPU baseline on a bounded sample ----
     cpu = None
@@ -321,7 +378,8 @@ def run_single(args, w):
         "gpu_launches": int(launches), "stage_ms": stage_ms, "active_experts": active,
         "ffn_useful_tflops": 6.0 * T * D * F / ((stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) * 1e-3) / 1e12
         if (stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) > 0 else None,
-        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clock_summary,
+        "routing_vs_other_orders": routing_differences(w, x, cent, ln, gate, torch) if not args.no_cpu else None,
     }
     layer.terminate()
     if not args.no_cpu:

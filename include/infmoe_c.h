@@ -207,7 +207,10 @@ INFMOE_API int infmoe_expert_select(int64_t token_num, int32_t expert_count, con
 
 /* moe_expert_count (plugin/cuda/moe.cu:161-212), on the device: d_count[E],
  * d_offset[E+1] (offset[E] = T, plugin/MoELayerPlugin.cc:351), d_pos[T] in the
- * reference's stable order. */
+ * reference's stable order.  A gate outside [0, E) (the reference asserts,
+ * moe.cu:184) sets bit 1 of d_status; such tokens are listed, in ascending order,
+ * behind the tokens of the last expert, and d_offset[E] is the number of tokens
+ * that do have an expert, so d_pos is always a permutation of 0..T-1. */
 INFMOE_API int infmoe_expert_count(int64_t token_num, int32_t expert_count, const int32_t* d_gate, int32_t* d_pos,
                                    int32_t* d_count, int32_t* d_offset, int32_t* d_status, void* stream);
 
@@ -234,20 +237,23 @@ INFMOE_API int infmoe_gelu_dot(const float* d_a, float* d_b, size_t len, void* s
 
 /* T5FFLayer::run for one expert (plugin/sublayers/T5FFLayer.cc:90-141) on
  * `rows` rows: d_y = d_x + (gelu(LN(x) wi0^T) * (LN(x) wi1^T)) wo^T.  Weights are
- * plain FP32 device arrays.  d_workspace must hold infmoe_t5ff_workspace_bytes. */
+ * plain FP32 device arrays.  d_workspace must hold infmoe_t5ff_workspace_bytes.
+ * Blocks the host until the result is there (like the reference's run, which ends
+ * in a stream synchronisation) and returns the device-side status. */
 INFMOE_API int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t embedding_size, int32_t hidden_size, size_t* bytes);
 INFMOE_API int infmoe_t5ff_run(int64_t rows, int32_t embedding_size, int32_t hidden_size, const float* d_ln_w,
                                const float* d_wi0, const float* d_wi1, const float* d_wo, const float* d_x,
                                float* d_y, void* d_workspace, size_t workspace_bytes, void* stream);
 
-/* The same expert FFN for callers that cannot allocate device memory -- a TensorRT
- * plugin inside enqueue(), code that runs while a CUDA graph is being captured, a
- * serving loop that may not risk the device-wide synchronisation of cudaMalloc.
- * It has no counterpart in the reference: it is infmoe_t5ff_run without the
- * workspace argument.  All scratch lives in an array that is part of the library
- * image (32 MiB, held by every GPU that loads the library until the process
- * exits); the call performs no cudaMalloc / cudaFree and uses no allocating
- * library routine.
+/* The same expert FFN for callers that cannot allocate device memory at the
+ * moment they need it: a TensorRT plugin inside enqueue(), whose engine fixed its
+ * memory plan when it was built, and a serving loop that may not risk the
+ * device-wide synchronisation a cudaMalloc can cause.  It has no counterpart in
+ * the reference: it is infmoe_t5ff_run without the workspace argument.  All
+ * scratch lives in an array that is part of the library image (32 MiB, held by
+ * every GPU that loads the library until the process exits); the call performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.  Like
+ * infmoe_t5ff_run it blocks the host until the result is there.
  *   - Sizes whose scratch need (infmoe_t5ff_workspace_bytes) exceeds the array are
  *     rejected with INFMOE_ERR_UNSUPPORTED; infmoe_t5ff_static_limit reports both
  *     numbers.  Examples that fit: d_model 512, d_ff 1024, 256 rows; d_model 1024,

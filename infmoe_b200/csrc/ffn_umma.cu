@@ -273,7 +273,8 @@ struct GemmArgs {
     int K;
     float* out_hi;              // GELU_PAIR: g_hi [T][M_total / 2]; RESIDUAL: y [T][M_total]
     float* out_lo;              // GELU_PAIR: g_lo
-    const float* resid;         // RESIDUAL: x [T][M_total]
+    const float* resid;         // RESIDUAL: the rows the experts were applied to, indexed like the output: row
+                                // out_pos[j] (or j) of x [rows][M_total]; no routed copy of x is needed
     const int* out_pos;         // RESIDUAL: row j is written to row out_pos[j] of y (NULL: row j), i.e. the combine
                                 // step moe_expert_gather (plugin/cuda/moe.cu:89-96) fused into the epilogue
     const float* mix_score;     // RESIDUAL: routed scores for the base_layer output mix (NULL: no mix)
@@ -307,17 +308,21 @@ __device__ __forceinline__ void chunking(int cnt, int& nch, int& csz) {
     csz = nch ? (((cnt + nch - 1) / nch + 15) & ~15) : 0;  // balanced chunks, multiple of 16, <= NMAX
 }
 
+// Tiles are listed by expert in order of falling token count (s_order: list position -> expert, s_prefix: first
+// tile of each list position), so the long tiles of the busiest experts are handed out first and the short ones
+// fill the end of the schedule.
 template <int NMAX>
-__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, const GemmArgs& a) {
-    int lo = a.e_begin, hi = a.e_end - 1;  // last e with s_prefix[e] <= tile
+__device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, const short* s_order, const GemmArgs& a) {
+    int lo = 0, hi = a.E - 1;  // last list position with s_prefix[.] <= tile
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
         if (s_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
     }
     TileInfo t;
-    t.expert = lo;
-    t.slot = a.slot_of_expert ? a.slot_of_expert[lo] : lo;
-    const int beg = a.offset[lo], cnt = a.offset[lo + 1] - beg;
+    const int ex = s_order[lo];
+    t.expert = ex;
+    t.slot = a.slot_of_expert ? a.slot_of_expert[ex] : ex;
+    const int beg = a.offset[ex], cnt = a.offset[ex + 1] - beg;
     int nch, csz;
     chunking<NMAX>(cnt, nch, csz);
     const int local = tile - s_prefix[lo];
@@ -327,6 +332,13 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, const int* s_prefix, c
     t.n_tok = min(csz, beg + cnt - t.row0);
     t.n_pad = (t.n_tok + 15) & ~15;
     return t;
+}
+
+// Tile of this CTA in round j of the schedule: the CTAs walk the list forwards in even rounds and backwards in odd
+// ones, so that over two rounds every CTA gets one tile from each end of a stretch of the (sorted) list.
+__device__ __forceinline__ int tile_of_round(int j) {
+    const int G = (int)gridDim.x, b = (int)blockIdx.x;
+    return j * G + ((j & 1) ? G - 1 - b : b);
 }
 
 template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
@@ -348,6 +360,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_prefix[MAX_EXPERTS + 1];
+    __shared__ int s_cnt[MAX_EXPERTS];
+    __shared__ short s_order[MAX_EXPERTS];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -356,15 +370,28 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int MB = (args.M_total + UMMA_M - 1) / UMMA_M;
     const int KB = (args.K + BK - 1) / BK;
 
-    // ---- tile schedule: exclusive prefix of tiles per expert -------------------------------
+    // ---- tile schedule: experts by falling token count, exclusive prefix of their tiles ---------
+    for (int e = threadIdx.x; e < args.E; e += GEMM_THREADS)
+        s_cnt[e] = (e >= args.e_begin && e < args.e_end) ? args.offset[e + 1] - args.offset[e] : 0;
+    __syncthreads();
+    for (int e = threadIdx.x; e < args.E; e += GEMM_THREADS) {
+        const int c = s_cnt[e];
+        int rank = 0;   // experts that come before e: more tokens, or as many and a lower index
+        for (int o = 0; o < args.E; ++o) {
+            const int co = s_cnt[o];
+            rank += (co > c || (co == c && o < e)) ? 1 : 0;
+        }
+        s_order[rank] = (short)e;
+    }
+    __syncthreads();
     if (warp == 0) {
         int carry = 0;
         for (int e0 = 0; e0 < args.E; e0 += 32) {
-            const int e = e0 + lane;
+            const int e = e0 + lane;   // list position
             int nt = 0;
-            if (e < args.E && e >= args.e_begin && e < args.e_end) {
+            if (e < args.E) {
                 int nch, csz;
-                chunking<NMAX>(args.offset[e + 1] - args.offset[e], nch, csz);
+                chunking<NMAX>(s_cnt[s_order[e]], nch, csz);
                 nt = nch * MB;
             }
             int incl = nt;
@@ -416,8 +443,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // Runs up to W_STAGES k blocks ahead of the transform warps, independently of the token ring.
         if (lane == 0) {
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+            for (int round = 0, tile; (tile = tile_of_round(round)) < total_tiles && !*abort_flag; ++round) {
+                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, s_order, args);
                 bool ok = true;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % W_STAGES;
@@ -433,8 +460,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ================= TMA producer, tokens (head and tail planes) =================
         if (lane == 0) {
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+            for (int round = 0, tile; (tile = tile_of_round(round)) < total_tiles && !*abort_flag; ++round) {
+                const TileInfo t = decode_tile<NMAX>(tile, s_prefix, s_order, args);
                 // one box of n_pad rows per plane (rows past the chunk's tokens belong to the next expert or are
                 // zero-filled past the end; they only feed accumulator columns that are never stored)
                 const CUtensorMap* map_hi = &token_maps.hi[(t.n_pad >> 4) - 1];
@@ -467,8 +494,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const uint32_t d = tmem_base + mine * ACC_STRIDE;
         const uint32_t acc_empty = smem_u32(&s_acc_empty[mine]), acc_full = smem_u32(&s_acc_full[mine]);
         uint32_t it = 0, rounds = 0;   // rounds: hand-overs of this issuer's accumulator so far
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+        for (int round = 0, tile; (tile = tile_of_round(round)) < total_tiles && !*abort_flag; ++round) {
+            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, s_order, args);
             const uint32_t idesc_tf32 = make_idesc(t.n_pad, 2u), idesc_bf16 = make_idesc(t.n_pad, 1u);
             bool ok = true, entered = false;   // entered: the accumulator has been taken over for the current chunk
             for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -523,8 +550,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         mbar_arrive(smem_u32(&s_acc_empty[0]));
         mbar_arrive(smem_u32(&s_acc_empty[1]));
         uint32_t it = 0, rounds0 = 0, rounds1 = 0;      // rounds: hand-overs of accumulator 0 / 1 so far
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, args);
+        for (int round = 0, tile; (tile = tile_of_round(round)) < total_tiles && !*abort_flag; ++round) {
+            const TileInfo t = decode_tile<NMAX>(tile, s_prefix, s_order, args);
             const int nsl = t.n_pad >> 4;
             float sum[C::SLICES][16];
 #pragma unroll
@@ -582,6 +609,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const float v = sum[i][c];
                     const unsigned long long out_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_ptr, c) : 0ull;
                     const float alpha = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_alpha, c) : 0.f;
+                    const int resid_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_row, c) : 0;
                     if (EPI == EPI_GELU_PAIR) {
                         // even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index
                         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
@@ -604,9 +632,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         }
                     } else {
                         if (col < t.n_tok && m_ok) {
-                            const int row = t.row0 + col;
-                            const size_t o = (size_t)row * (size_t)args.M_total + (size_t)m;
-                            const float x = args.resid[o];
+                            const float x = args.resid[(size_t)resid_row * (size_t)args.M_total + (size_t)m];
                             float y = __fadd_rn(x, v);
                             if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
                             reinterpret_cast<float*>(out_row)[m] = y;
@@ -628,7 +654,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // handed back to the producer) right after the buffer of k block `it` has been handed to the MMA
         // issuers, i.e. while this warp would otherwise wait for the next TMEM buffer to come free.
         int my_tiles = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) ++my_tiles;
+        for (int round = 0; tile_of_round(round) < total_tiles; ++round) ++my_tiles;
         const uint32_t total_it = (uint32_t)my_tiles * (uint32_t)KB;
         float4 v[8];
         bool ok = total_it > 0 && !*abort_flag;
@@ -785,7 +811,7 @@ template <int EPI, int NMAX, int W_STAGES, int T_STAGES>
 int launch_one(const GemmArgs& args, long long T, int slots, const float* w, const float* a_hi, const float* a_lo,
                int num_ctas, cudaStream_t stream) {
     using C = Cfg<NMAX, W_STAGES, T_STAGES>;
-    static_assert(C::SMEM + 8192 <= 227 * 1024, "shared-memory rings too large");
+    static_assert(C::SMEM + 12288 <= 227 * 1024, "shared-memory rings too large");
     static_assert(NMAX <= 16 * TOKEN_BOXES, "a token tile needs a tensor map of its height");
     CUtensorMap map_w;
     TokenMaps tm;

@@ -11,19 +11,25 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
                  float* score, int* status, cudaStream_t stream);
 int launch_select_top1(long long T, int E, const float* aff, int* gate, float* weight, int* status,
                        cudaStream_t stream);
+// region_count != NULL: the T slots are regions of region_size slots, of which only the first region_count[s]
+// hold rows (receive buffer of the expert-parallel path); the other slots are skipped silently.
 int launch_dispatch(const int* gate, long long T, int E, int* pos, int* count, int* offset, int* status,
-                    cudaStream_t stream);
+                    cudaStream_t stream, const int* region_count = nullptr, int region_size = 0);
 int launch_scatter(long long T, int D, const float* X, const float* coeff, const int* pos, float* routed,
                    float* rcoeff, cudaStream_t stream);
+// valid_rows (device, may be NULL): rows at or past *valid_rows are skipped (tokens without an expert sit at
+// the tail of pos[]; the dispatch kernel stores their start in offset[E]).  routed may be NULL.
 int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
-                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo, bool pack,
-                            cudaStream_t stream);
-int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream);
+                            const float* gamma_all, const int* valid_rows, float* routed, float* rscore, float* h_hi,
+                            float* h_lo, bool pack, cudaStream_t stream);
+int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream,
+                  const int* valid_rows = nullptr);
 int launch_mix_gather(long long T, int D, const int* pos, const float* routed, const float* post,
-                      const float* coeff, float* out, cudaStream_t stream);
+                      const float* coeff, float* out, cudaStream_t stream, const int* valid_rows = nullptr);
 int launch_layernorm(float* out, const float* in, long long n, int D, const float* gamma, cudaStream_t stream);
 int launch_gelu_dot(const float* a, float* b, size_t len, cudaStream_t stream);
 int launch_split(const float* src, float* hi, float* lo, size_t len, cudaStream_t stream);
+int launch_fill_int(int* dst, int value, cudaStream_t stream);   // *dst = value, stream ordered
 // Tile-contiguous weight layout (see rows.cu); src1 != NULL interleaves the rows of two matrices.
 int launch_retile(const float* src0, const float* src1, int M, int K, float* dst, cudaStream_t stream);
 inline size_t tiled_elems(int M, int K) { return (size_t)((M + 127) / 128) * 128 * (size_t)((K + 31) / 32) * 32; }

@@ -71,6 +71,11 @@ struct ExpertStore {
     std::vector<char> on_device;
     std::vector<unsigned> version;   // bumped whenever an expert's host weights are replaced (expert caches compare it)
     bool fortran_warning = false;
+    // Recorded behind the copies and retile kernels of the last upload_resident, on the stream that ran them.
+    // Clones share this store and enqueue on streams of their own: each of them waits for the event before its
+    // GEMMs read the planes, and the next upload waits for it before it reuses d_staging.
+    cudaEvent_t ev_uploaded = nullptr;
+    bool upload_recorded = false;
 
     size_t matrix_elems() const { return (size_t)D * (size_t)F; }
     size_t plane_elems(int p) const { return p == 0 ? tiled_elems(2 * F, D) : tiled_elems(D, F); }   // per expert
@@ -84,6 +89,7 @@ struct ExpertStore {
         for (float* p : d_plane)
             if (p) cudaFree(p);
         if (d_staging) cudaFree(d_staging);
+        if (ev_uploaded) cudaEventDestroy(ev_uploaded);
     }
 };
 
@@ -177,6 +183,8 @@ int parse_flags(const char* variant, Flags* f) {
     return INFMOE_OK;
 }
 
+bool uses_umma(const infmoe_layer* L) { return L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E); }
+
 WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     WsLayout w{};
     size_t o = 0;
@@ -193,8 +201,11 @@ WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     w.slot_map = take(4 * E);
     w.score = take(4 * t);
     w.rscore = take(4 * t);
-    w.routed = take(4 * t * D);
-    w.post = take(4 * t * D);
+    // The tensor-core GEMM reads its residual from the input through pos[] and writes the layer output from its
+    // epilogue; only the CUDA-core path and the Identity sublayer keep routed rows and expert-ordered results.
+    const bool row_planes = L->identity || !uses_umma(L);
+    w.routed = take(row_planes ? 4 * t * D : 0);
+    w.post = take(row_planes ? 4 * t * D : 0);
     w.h_hi = take(4 * t * D);
     w.h_lo = take(second_plane_bytes((long long)t, L->D));
     w.g_hi = take(4 * t * F);
@@ -253,8 +264,13 @@ int load_expert_planes(int D, int F, const float* wi0, const float* wi1, const f
 }
 
 // Uploads every expert that is on the host but not yet on the device.
+// Called with the store's lock held.  Whatever stream the caller works on, it leaves this function ordered behind
+// every upload queued so far (by itself or by a clone on another stream).
 int upload_resident(ExpertStore* s, cudaStream_t stream) {
     INFMOE_TRY(ensure_resident_planes(s));
+    if (!s->ev_uploaded) INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&s->ev_uploaded, cudaEventDisableTiming));
+    if (s->upload_recorded) INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, s->ev_uploaded, 0));
+    bool queued = false;
     for (int e = 0; e < s->E; ++e) {
         if (s->on_device[e] || !s->on_host[e]) continue;
         if (!s->d_staging) INFMOE_CUDA_TRY(cudaMalloc(&s->d_staging, sizeof(float) * 3 * s->matrix_elems()));
@@ -262,6 +278,11 @@ int upload_resident(ExpertStore* s, cudaStream_t stream) {
                                       s->d_plane[0] + s->plane_elems(0) * e, s->d_plane[1] + s->plane_elems(1) * e,
                                       true, s->d_staging, stream));
         s->on_device[e] = 1;
+        queued = true;
+    }
+    if (queued) {
+        INFMOE_CUDA_TRY(cudaEventRecord(s->ev_uploaded, stream));
+        s->upload_recorded = true;
     }
     return INFMOE_OK;
 }
@@ -299,8 +320,6 @@ int ensure_device(infmoe_layer* L) {
         INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&L->ev_freed[i], cudaEventDisableTiming));
     }
     INFMOE_CUDA_TRY(cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming));
-    const char* path = getenv("INFMOE_FFN");
-    if (path && strcmp(path, "simt") == 0) L->ffn_path = 1;
     L->device_ready = true;
     return INFMOE_OK;
 }
@@ -359,8 +378,6 @@ struct FfnOutput {
     const float* mix_score = nullptr;
     const unsigned long long* row_ptr = nullptr;   // address of output row i instead of out + i * D
 };
-
-bool uses_umma(const infmoe_layer* L) { return L->ffn_path == 0 && ffn_umma_supported(L->D, L->F, L->E); }
 
 int run_ffn(infmoe_layer* L, long long T, int e_begin, int e_end, const int* d_offset, const int* d_slot_map,
             int slots, float* const planes[2], const float* h_hi, const float* h_lo, const float* routed, float* g_hi,
@@ -494,6 +511,9 @@ int infmoe_layer_create(const infmoe_layer_config* cfg, infmoe_layer** out) {
     L->identity = identity;
     L->store = make_store(L->E, L->D, L->F);
     L->launches_at_create = g_kernel_launches;
+    // decided here, not at the first enqueue: the workspace size depends on it
+    const char* path = getenv("INFMOE_FFN");
+    if (path && strcmp(path, "simt") == 0) L->ffn_path = 1;
     *out = L;
     return INFMOE_OK;
 }
@@ -518,6 +538,7 @@ int infmoe_layer_clone(const infmoe_layer* src, infmoe_layer** out) {
     L->store = src->store;  // shared, like the reference's sublayer
     L->residency = src->residency;
     L->initialized = src->initialized;
+    L->ffn_path = src->ffn_path;
     L->launches_at_create = g_kernel_launches;
     *out = L;
     return INFMOE_OK;
@@ -812,9 +833,12 @@ int infmoe_layer_workspace_bytes(const infmoe_layer* L, int64_t T, size_t* bytes
 // caller-provided expert index per row it runs dispatch + experts only and returns every row's expert
 // output in the caller's row order (no score mix): the building block of the expert-parallel path, where
 // routing happened on the rank that owns the token.
+// region_count / region_size (expert-parallel receive buffer): the T rows are slots in regions of region_size, of
+// which only the first region_count[s] of region s hold a row.
 static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_ws, size_t ws_bytes, int64_t T,
                      void* stream_v, const int* given_gate, const float* row_score = nullptr,
-                     const unsigned long long* row_dst = nullptr) {
+                     const unsigned long long* row_dst = nullptr, const int* region_count = nullptr,
+                     int region_size = 0) {
     if (!L || T < 0 || (T > 0 && (!d_in || (!d_out && !row_dst) || !d_ws))) {
         set_error("layer_enqueue: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
@@ -880,7 +904,8 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
                                 L->D, L->E, gate, score, L->d_status, stream));
     INFMOE_TRY(prof_mark(L, 1, stream));
     // 2. dispatch metadata (:350-352)
-    INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream));
+    INFMOE_TRY(launch_dispatch(gate_in, T, L->E, pos, count, offset, L->d_status, stream, region_count, region_size));
+    const int* valid_rows = offset + L->E;   // rows past it have no expert (or are empty slots): nobody touches them
     INFMOE_TRY(prof_mark(L, 2, stream));
     // whole layer: the variant decides; experts alone: the caller asks for the mix by passing the scores
     const bool mix = given_gate ? row_score != nullptr : L->flags.base_layer_mix;
@@ -901,8 +926,11 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
         const bool pack = uses_umma(L);   // the GEMM run_ffn picks
-        INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate_in, s->d_ln, routed, rscore, h_hi, h_lo,
-                                           pack, stream));
+        // tensor-core path: no routed copy, the second GEMM's epilogue reads its residual from d_in through pos[]
+        if (pack) routed = nullptr;
+        INFMOE_TRY(launch_scatter_ln_split(T, L->D, d_in, score, pos, gate_in, s->d_ln, valid_rows, routed, rscore,
+                                           h_hi, h_lo, pack, stream));
+        if (pack) routed = const_cast<float*>(d_in);   // run_ffn's residual operand
         INFMOE_TRY(prof_mark(L, 3, stream));
         // 4. experts (:360-402)
         if (!streamed) {
@@ -998,9 +1026,9 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
         // T x d_ff floats), then copied out
         float* ordered = row_dst ? g_hi : d_out;
         if (mix)
-            INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, ordered, stream));
+            INFMOE_TRY(launch_mix_gather(T, L->D, pos, routed, post, rscore, ordered, stream, valid_rows));
         else
-            INFMOE_TRY(launch_gather(T, L->D, post, pos, ordered, stream));
+            INFMOE_TRY(launch_gather(T, L->D, post, pos, ordered, stream, valid_rows));
         if (row_dst) INFMOE_TRY(launch_rows_to_ptrs(T, L->D, ordered, row_dst, stream));
     }
     INFMOE_TRY(prof_mark(L, 6, stream));
@@ -1379,6 +1407,60 @@ int infmoe_gelu_dot(const float* a, float* b, size_t len, void* stream) {
     return launch_gelu_dot(a, b, len, (cudaStream_t)stream);
 }
 
+}  // extern "C"
+
+namespace {
+
+// One expert's FFN with all scratch carved from `base` (256-byte aligned, infmoe_t5ff_workspace_bytes long):
+// the body shared by infmoe_t5ff_run (caller's workspace) and infmoe_t5ff_run_static (the library's own array).
+// Everything it reads from the scratch it writes first (offsets, activation planes, weight planes), and it
+// clears its status word, so leftovers of an earlier call do not matter.  Blocks until the stream is idle and
+// returns the device-side status.
+int t5ff_run_in(char* base, int64_t rows, int32_t D, int32_t F, const float* ln_w, const float* wi0, const float* wi1,
+                const float* wo, const float* x, float* y, cudaStream_t stream) {
+    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
+    char* p = base;
+    auto take = [&](size_t bytes) {
+        char* at = p;
+        p += align_up(bytes);
+        return at;
+    };
+    float* h_hi = (float*)take(4 * r * d);
+    float* h_lo = (float*)take(second_plane_bytes(rows, D));
+    float* g_hi = (float*)take(4 * r * f);
+    float* g_lo = (float*)take(second_plane_bytes(rows, F));
+    float* planes[2];
+    planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
+    planes[1] = (float*)take(4 * tiled_elems(D, F));
+    int* offset = (int*)take(8);
+    int* status = (int*)take(4);
+    // offset[] = {0, rows}: the row count travels as a kernel parameter, so no host buffer has to outlive the call
+    INFMOE_CUDA_TRY(cudaMemsetAsync(offset, 0, 4, stream));
+    INFMOE_TRY(launch_fill_int(offset + 1, (int)rows, stream));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    const char* path = getenv("INFMOE_FFN");
+    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
+    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, !simt, stream));
+    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
+    int dev = 0, sms = 0;
+    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
+    INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (simt)
+        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
+                                   y, stream));
+    else
+        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], x, g_hi,
+                                   g_lo, y, status, sms, stream));
+    int h_status = 0;
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+    return status_to_rc(h_status);
+}
+
+}  // namespace
+
+extern "C" {
+
 int infmoe_t5ff_workspace_bytes(int64_t rows, int32_t D, int32_t F, size_t* bytes) {
     if (!bytes || rows < 0 || D <= 0 || F <= 0) {
         set_error("t5ff_workspace_bytes: bad argument");
@@ -1404,43 +1486,8 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
         set_error("t5ff_run: workspace of %zu bytes is too small, %zu needed", ws_bytes, need);
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
-    cudaStream_t stream = (cudaStream_t)stream_v;
-    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    char* p = (char*)(((uintptr_t)ws + ALIGN - 1) / ALIGN * ALIGN);
-    auto take = [&](size_t bytes) {
-        char* at = p;
-        p += align_up(bytes);
-        return at;
-    };
-    float* h_hi = (float*)take(4 * r * d);
-    float* h_lo = (float*)take(second_plane_bytes(rows, D));
-    float* g_hi = (float*)take(4 * r * f);
-    float* g_lo = (float*)take(second_plane_bytes(rows, F));
-    float* planes[2];
-    planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
-    planes[1] = (float*)take(4 * tiled_elems(D, F));
-    int* offset = (int*)take(8);
-    int* status = (int*)take(4);
-    const int h_offset[2] = {0, (int)rows};
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
-    INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    const char* path = getenv("INFMOE_FFN");
-    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
-    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, !simt, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
-    int dev = 0, sms = 0;
-    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
-    INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    if (simt)
-        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
-                                   y, stream));
-    else
-        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], x, g_hi,
-                                   g_lo, y, status, sms, stream));
-    int h_status = 0;
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
-    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
-    return status_to_rc(h_status);
+    char* base = (char*)(((uintptr_t)ws + ALIGN - 1) / ALIGN * ALIGN);
+    return t5ff_run_in(base, rows, D, F, ln_w, wi0, wi1, wo, x, y, (cudaStream_t)stream_v);
 }
 
 }  // extern "C"
@@ -1448,15 +1495,16 @@ int infmoe_t5ff_run(int64_t rows, int32_t D, int32_t F, const float* ln_w, const
 // =================================================================================================
 // Expert FFN for callers that must not allocate
 // =================================================================================================
-// A TensorRT plugin's enqueue(), code running while a CUDA graph is being captured, and serving
-// loops with a hard latency budget may not call cudaMalloc: the call can synchronise the whole
-// device, is refused during capture, and would break an engine whose memory plan was fixed when
-// it was built.  infmoe_t5ff_run needs a caller-provided workspace, which such a caller has to
+// Two kinds of caller may not call cudaMalloc at the moment they need an expert FFN: a TensorRT
+// plugin inside enqueue(), whose engine fixed its memory plan when it was built, and a serving loop
+// with a hard latency budget, for which the device-wide synchronisation an allocation can cause is
+// not acceptable.  infmoe_t5ff_run needs a caller-provided workspace, which such a caller has to
 // have planned for in advance.  infmoe_t5ff_run_static needs none: its scratch (LayerNorm output,
 // gate activations, the row-interleaved copy of the weight matrices) lives in the array
 // below, which is part of the library image.  Every GPU that loads the library keeps these
 // INFMOE_STATIC_SCRATCH_BYTES resident until the process exits, so the size is deliberately modest;
-// larger problems are rejected and belong to infmoe_t5ff_run.
+// larger problems are rejected and belong to infmoe_t5ff_run.  Like infmoe_t5ff_run the call
+// blocks the host until the result is there.
 #define INFMOE_STATIC_SCRATCH_BYTES (32u << 20)
 static __device__ __align__(256) unsigned char g_static_scratch[INFMOE_STATIC_SCRATCH_BYTES];
 
@@ -1518,45 +1566,8 @@ int infmoe_t5ff_run_static(int64_t rows, int32_t D, int32_t F, const float* ln_w
     }
     unsigned char* scratch = nullptr;
     INFMOE_TRY(static_scratch_address(&scratch));
-    cudaStream_t stream = (cudaStream_t)stream_v;
-    const size_t r = (size_t)rows, d = (size_t)D, f = (size_t)F;
-    char* p = (char*)scratch;   // the array is 256-byte aligned already
-    auto take = [&](size_t bytes) {
-        char* at = p;
-        p += align_up(bytes);
-        return at;
-    };
-    float* h_hi = (float*)take(4 * r * d);
-    float* h_lo = (float*)take(second_plane_bytes(rows, D));
-    float* g_hi = (float*)take(4 * r * f);
-    float* g_lo = (float*)take(second_plane_bytes(rows, F));
-    float* planes[2];
-    planes[0] = (float*)take(4 * tiled_elems(2 * F, D));
-    planes[1] = (float*)take(4 * tiled_elems(D, F));
-    int* offset = (int*)take(8);
-    int* status = (int*)take(4);
-    // The array keeps whatever the previous call left: everything read below is rewritten first
-    // (offsets, both activation planes, all weight planes); only the status word must start at zero.
-    const int h_offset[2] = {0, (int)rows};
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(offset, h_offset, sizeof(h_offset), cudaMemcpyHostToDevice, stream));
-    INFMOE_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    const char* path = getenv("INFMOE_FFN");
-    const bool simt = (path && strcmp(path, "simt") == 0) || !ffn_umma_supported(D, F, 1);
-    INFMOE_TRY(launch_ln_split(rows, D, x, ln_w, h_hi, h_lo, !simt, stream));
-    INFMOE_TRY(load_expert_planes(D, F, wi0, wi1, wo, planes[0], planes[1], false, nullptr, stream));
-    int dev = 0, sms = 0;
-    INFMOE_CUDA_TRY(cudaGetDevice(&dev));
-    INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    if (simt)
-        INFMOE_TRY(launch_ffn_simt(rows, D, F, 0, 1, offset, nullptr, h_hi, h_lo, planes[0], planes[1], x, g_hi, g_lo,
-                                   y, stream));
-    else
-        INFMOE_TRY(launch_ffn_umma(rows, D, F, 1, 0, 1, offset, nullptr, 1, h_hi, h_lo, planes[0], planes[1], x, g_hi,
-                                   g_lo, y, status, sms, stream));
-    int h_status = 0;
-    INFMOE_CUDA_TRY(cudaMemcpyAsync(&h_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
-    INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
-    return status_to_rc(h_status);
+    // the array is 256-byte aligned already
+    return t5ff_run_in((char*)scratch, rows, D, F, ln_w, wi0, wi1, wo, x, y, (cudaStream_t)stream_v);
 }
 
 }  // extern "C"

@@ -17,6 +17,7 @@
 #include <zlib.h>
 
 #include <cstdio>
+#include <cstdint>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -52,7 +53,9 @@ int parse_npy_dict(const std::string& h, std::string& descr, bool& fortran, std:
     if (p == std::string::npos) return INFMOE_ERR_FORMAT;
     p = h.find(':', p);
     if (p == std::string::npos) return INFMOE_ERR_FORMAT;
-    fortran = h.compare(h.find_first_not_of(" ", p + 1), 4, "True") == 0;
+    const size_t v = h.find_first_not_of(" ", p + 1);
+    if (v == std::string::npos) return INFMOE_ERR_FORMAT;
+    fortran = h.compare(v, 4, "True") == 0;
     p = h.find("'shape'");
     if (p == std::string::npos) return INFMOE_ERR_FORMAT;
     p = h.find('(', p);
@@ -217,7 +220,13 @@ int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order)
             }
         }
         size_t count = 1;
-        for (int64_t d : shape) count *= (size_t)d;
+        for (int64_t d : shape) {
+            if (d < 0 || (d > 0 && count > (SIZE_MAX / sizeof(float)) / (size_t)d)) {
+                set_error("%s: member %s has a shape whose element count overflows", path, name.c_str());
+                return INFMOE_ERR_FORMAT;
+            }
+            count *= (size_t)d;
+        }
         float* dst = nullptr;
         const int rc = alloc(name, shape, &dst);
         if (rc != INFMOE_OK) return rc;

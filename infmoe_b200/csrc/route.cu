@@ -6,24 +6,32 @@
 //   cublasSgemm_v2       plugin/MoELayerPlugin.cc:334-336  (aff = Xs * C^T)
 //   moe_expert_select    plugin/cuda/moe.cu:147-159     (strict '>' scan, first maximum wins)
 //
-// Layout: X [T][D], centroids [E][D], both row-major FP32.  A CTA owns 4 * TW tokens (TPW = 4 per
-// warp; TW token warps, picked per launch so that the CTAs fill whole waves of the SMs).  With more
-// than one group of EG experts the CTA has two such sets of warps ("halves"): both work on the same
-// tokens, half h takes the expert groups h, h + 2, ..., and their winners are merged at the end, which
-// doubles the warps that hide each other's latencies.  The rows of X are read from global memory one 128-float step
-// ahead of their use.  Centroids are streamed through shared memory in
-// tiles of EG experts x KT floats with double-buffered cp.async, so every
-// centroid byte is fetched from L2 once per CTA and every LDS.128 feeds
-// 4 * TPW fused multiply-adds; a warp keeps TPW * EG per-lane partial sums in
-// registers.  The per-(token, expert) summation order does not depend on the
-// blocking, so the result is the canonical order of common.cuh bit for bit.
-// All arithmetic is explicit round-to-nearest FP32 (no tensor cores).
+// Layout: X [T][D], centroids [E][D], both row-major FP32.  All arithmetic is explicit
+// round-to-nearest FP32 (no tensor cores), in the canonical order of common.cuh: the score of
+// (token, expert) is the butterfly sum of 32 partial sums, partial l running over the elements
+// k = 128 i + 4 l + c (i ascending, c = 0..3) with fused multiply-adds.
+//
+// The 32 partial sums are 32 independent small matrix products, and the kernel is blocked like
+// one.  A CTA of 16 warps owns 32 tokens and walks over the experts 32 at a time.  Half a warp
+// works on one partial index l (lanes 0-15: l = warp, lanes 16-31: l = warp + 16); its 16 threads
+// tile the 32 tokens x 32 experts as 4 x 4 threads with 8 x 8 accumulators each.  Per 128-float
+// step of the row a thread reads 8 token values and 8 centroid values (one 128-bit shared-memory
+// load each, every load shared by four lanes) for 256 fused multiply-adds, so neither the
+// shared-memory pipe nor the instruction issue limits the FP32 pipe.  Rows and centroids are
+// staged through shared memory with cp.async, 256 floats per row and stage, double buffered; the
+// LayerNorm is applied once per staged value, in place, by the thread that fetched it.  After the
+// last stage the partial sums of l and l + 16 are combined by a shuffle (the butterfly's first
+// step), the other 16 go through shared memory, and a warp per token finishes the butterfly and
+// the argmax.
+//
+// Shared-memory tiles: [stage][step][row][slot] of 16-byte chunks, slot = l ^ (row & 3) ^ (4 if
+// l >= 16): consecutive l of one row fill one 512-byte line (conflict-free staging), and the eight
+// chunks a warp reads at once (4 rows x 2 values of l) fall into eight different bank groups.
 #include "common.cuh"
 
 namespace infmoe {
 
 namespace {
-
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -33,203 +41,205 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Fills one shared-memory tile: experts [e0, e0+EG) x floats [k0, k0+KT) of the centroids, zero padded.
-template <int EG, int KT, int ROUTE_THREADS>
-__device__ __forceinline__ void load_centroid_tile(float* __restrict__ tile, const float* __restrict__ C, int E, int D,
-                                                   int e0, int k0, bool vec, int tid) {
-    if (vec) {
-        for (int idx = tid; idx < EG * (KT / 4); idx += ROUTE_THREADS) {
-            const int j = idx / (KT / 4), k = (idx % (KT / 4)) * 4;
-            float* dst = tile + j * KT + k;
-            if (e0 + j < E && k0 + k < D) cp_async16(dst, C + (long long)(e0 + j) * D + k0 + k);
-            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    } else {
-        for (int idx = tid; idx < EG * KT; idx += ROUTE_THREADS) {
-            const int j = idx / KT, k = idx % KT;
-            tile[idx] = (e0 + j < E && k0 + k < D) ? C[(long long)(e0 + j) * D + k0 + k] : 0.f;
-        }
-    }
-}
+constexpr int RT_TOKENS = 32;       // tokens per CTA
+constexpr int RT_EXPERTS = 32;      // experts per pass
+constexpr int RT_THREADS = 512;
+constexpr int RT_STEPS = 2;         // 128-float steps per stage
+constexpr int RT_STAGE_FLOATS = RT_STEPS * 128;
+constexpr int RT_STAGES = 2;
+constexpr int RT_TILE_CHUNKS = RT_STEPS * 32 * 32;             // 16-byte chunks of one tile (tokens or experts) of one stage
+constexpr int RT_SMEM = RT_STAGES * 2 * RT_TILE_CHUNKS * 16;   // token and centroid tiles
+constexpr int RT_RED_PITCH = 36;    // floats per token row of the partial-sum buffer (32 experts + padding)
+static_assert(16 * RT_TOKENS * RT_RED_PITCH * 4 <= RT_SMEM, "the partial sums reuse the tile memory");
 
-template <int TPW, int EG, int KT, int TW, int HALVES>
-__global__ void __launch_bounds__(TW * HALVES * 32)
+__device__ __forceinline__ int rt_slot(int l, int row) { return l ^ (row & 3) ^ ((l >> 4) << 2); }
+
+template <bool VEC>
+__global__ void __launch_bounds__(RT_THREADS, 1)
 route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
-             long long T, int D, int E, int vec, int* __restrict__ gate, float* __restrict__ score,
+             long long T, int D, int E, int* __restrict__ gate, float* __restrict__ score,
              int* __restrict__ status) {
-    constexpr int HALF_THREADS = TW * 32;
-    extern __shared__ __align__(16) float s_all_tiles[];   // [HALVES][2][EG][KT]
-    __shared__ float s_merge_score[TW][TPW];
-    __shared__ int s_merge_e[TW][TPW];
-    const int lane = threadIdx.x & 31;
-    const int half = (threadIdx.x >> 5) / TW;          // which set of expert groups this warp works on
-    const int warp = (threadIdx.x >> 5) % TW;          // which tokens
-    const int tid = threadIdx.x - half * HALF_THREADS; // thread index inside the half (tile loads)
-    float* const s_tiles = s_all_tiles + half * 2 * EG * KT;
-    const long long t0 = ((long long)blockIdx.x * TW + warp) * TPW;
-    const bool warp_live = t0 < T;   // whole warps past the end still help loading tiles
-
-    const float* rows[TPW];
-    float mean[TPW], rstd[TPW];
-    bool live[TPW];
-#pragma unroll
-    for (int i = 0; i < TPW; ++i) {
-        live[i] = t0 + i < T;
-        rows[i] = X + (live[i] ? (t0 + i) : (warp_live ? t0 : 0)) * (long long)D;  // dead slots alias a valid row
-        mean[i] = 0.f;
-        rstd[i] = 1.f;
-    }
+    extern __shared__ __align__(16) unsigned char rt_smem[];
+    float4* const xs = reinterpret_cast<float4*>(rt_smem);          // [stage][step][token][slot]
+    float4* const cs = xs + RT_STAGES * RT_TILE_CHUNKS;             // [stage][step][expert][slot]
+    float* const red = reinterpret_cast<float*>(rt_smem);           // [16][token][RT_RED_PITCH], after the last stage
+    __shared__ float s_mean[RT_TOKENS], s_rstd[RT_TOKENS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long t0 = (long long)blockIdx.x * RT_TOKENS;
     const bool use_ln = gamma != nullptr;
+
+    // row statistics, two tokens per warp
     if (use_ln) {
-        // row statistics once per token: half 0 computes them, the other half reads them from shared memory
-        if (warp_live && half == 0) {
-#pragma unroll
-            for (int i = 0; i < TPW; ++i) warp_row_stats(rows[i], D, vec != 0, mean[i], rstd[i]);
-        }
-        if (HALVES > 1) {
-            __shared__ float s_mean[TW][TPW], s_rstd[TW][TPW];
-            if (half == 0 && lane == 0) {
-#pragma unroll
-                for (int i = 0; i < TPW; ++i) {
-                    s_mean[warp][i] = mean[i];
-                    s_rstd[warp][i] = rstd[i];
-                }
-            }
-            __syncthreads();
-            if (half != 0) {
-#pragma unroll
-                for (int i = 0; i < TPW; ++i) {
-                    mean[i] = s_mean[warp][i];
-                    rstd[i] = s_rstd[warp][i];
+        for (int q = 0; q < 2; ++q) {
+            const int t = warp + 16 * q;
+            if (t0 + t < T) {
+                float mean, rstd;
+                warp_row_stats(X + (t0 + t) * (long long)D, D, VEC, mean, rstd);
+                if (lane == 0) {
+                    s_mean[t] = mean;
+                    s_rstd[t] = rstd;
                 }
             }
         }
     }
+    __syncthreads();
 
-    float best[TPW];
-    int best_e[TPW];
-#pragma unroll
-    for (int i = 0; i < TPW; ++i) {
-        best[i] = -FLT_MAX;   // reference plugin/cuda/moe.cu:26-27
-        best_e[i] = -1;
-    }
+    // compute role: partial index l, 8 tokens tt + 4 j, 8 experts te + 4 jj
+    const int l = warp + 16 * (lane >> 4);
+    const int tt = (lane >> 2) & 3, te = lane & 3;
+    // staging role: chunk (step, l) of rows rg + 8 r, r = 0..3
+    const int st_step = (tid & 63) >> 5, st_l = tid & 31, rg = tid >> 6;
+    const int st_k = st_step * 128 + st_l * 4;   // first float of my chunk inside a stage
 
-    const int ntiles = (D + KT - 1) / KT;
-    // The row values of step s (floats [128 s, 128 s + 128) of the row; lane l owns 4 of them) are fetched while
-    // step s - 1 is computed; after the last step of an expert group the first step of the next one follows.
-    float4 v_next[TPW], g_next = make_float4(1.f, 1.f, 1.f, 1.f);
-    auto fetch = [&](int base) {
-        if (base < D && warp_live) {
+    // stages of one pass over the row; tiles past the end of a row (or of the tokens / experts) are zero
+    const int nstages = (D + RT_STAGE_FLOATS - 1) / RT_STAGE_FLOATS;
+    auto issue = [&](int stage, int e0) {
+        const int buf = stage & 1;
+        const int k = stage * RT_STAGE_FLOATS + st_k;
+        float4* xt = xs + (buf * RT_STEPS + st_step) * 1024;
+        float4* ct = cs + (buf * RT_STEPS + st_step) * 1024;
 #pragma unroll
-            for (int i = 0; i < TPW; ++i) v_next[i] = load_row4(rows[i], base, D, vec != 0);
-            if (use_ln) g_next = load_row4(gamma, base, D, vec != 0);
+        for (int r = 0; r < 4; ++r) {
+            const int row = rg + 8 * r;
+            float4* xd = xt + row * 32 + rt_slot(st_l, row);
+            float4* cd = ct + row * 32 + rt_slot(st_l, row);
+            const bool x_ok = t0 + row < T && k < D, c_ok = e0 + row < E && k < D;
+            const float* xsrc = X + (t0 + row) * (long long)D + k;
+            const float* csrc = C + (long long)(e0 + row) * D + k;
+            if (VEC) {
+                if (x_ok) cp_async16(xd, xsrc); else *xd = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c_ok) cp_async16(cd, csrc); else *cd = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                *xd = x_ok ? load_row4(xsrc, 0, D - k, false) : make_float4(0.f, 0.f, 0.f, 0.f);
+                *cd = c_ok ? load_row4(csrc, 0, D - k, false) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     };
-    fetch(4 * lane);
-    // both halves run the same number of group passes (they share the CTA-wide barriers); a pass past the last
-    // group loads zero tiles and selects nothing
-    const int groups = (E + EG - 1) / EG, passes = (groups + HALVES - 1) / HALVES;
-    for (int pass = 0; pass < passes; ++pass) {
-        const int e0 = (pass * HALVES + half) * EG;
-        float acc[TPW][EG];
+    // LayerNorm of the token chunks this thread staged, in place; elements past the row stay zero
+    auto normalise = [&](int stage) {
+        const int buf = stage & 1;
+        const int k = stage * RT_STAGE_FLOATS + st_k;
+        if (k >= D) return;
+        const float4 g = load_row4(gamma, k, D, VEC);
+        float4* xt = xs + (buf * RT_STEPS + st_step) * 1024;
 #pragma unroll
-        for (int i = 0; i < TPW; ++i)
-#pragma unroll
-            for (int j = 0; j < EG; ++j) acc[i][j] = 0.f;
+        for (int r = 0; r < 4; ++r) {
+            const int row = rg + 8 * r;
+            if (t0 + row >= T) continue;
+            float4* xd = xt + row * 32 + rt_slot(st_l, row);
+            float4 v = *xd;
+            const float mean = s_mean[row], rstd = s_rstd[row];
+            v.x = ln_apply(v.x, mean, rstd, g.x);
+            v.y = k + 1 < D ? ln_apply(v.y, mean, rstd, g.y) : 0.f;
+            v.z = k + 2 < D ? ln_apply(v.z, mean, rstd, g.z) : 0.f;
+            v.w = k + 3 < D ? ln_apply(v.w, mean, rstd, g.w) : 0.f;
+            *xd = v;
+        }
+    };
 
-        load_centroid_tile<EG, KT, HALF_THREADS>(s_tiles, C, E, D, e0, 0, vec != 0, tid);
+    float best[2] = {-FLT_MAX, -FLT_MAX};   // reference plugin/cuda/moe.cu:26-27; tokens warp and warp + 16
+    int best_e[2] = {-1, -1};
+
+    for (int e0 = 0; e0 < E; e0 += RT_EXPERTS) {
+        float acc[8][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) acc[j][jj] = 0.f;
+
+        issue(0, e0);
         cp_async_commit();
-        for (int kt = 0; kt < ntiles; ++kt) {
-            const float* tile = s_tiles + (kt & 1) * EG * KT;
-            if (kt + 1 < ntiles)
-                load_centroid_tile<EG, KT, HALF_THREADS>(s_tiles + ((kt + 1) & 1) * EG * KT, C, E, D, e0, (kt + 1) * KT,
-                                                         vec != 0, tid);
+        for (int stage = 0; stage < nstages; ++stage) {
+            if (stage + 1 < nstages) issue(stage + 1, e0);
             cp_async_commit();
-            cp_async_wait<1>();   // tile kt has landed (the group of tile kt+1 may still be in flight)
-            __syncthreads();
-            if (warp_live && e0 < E) {
-#pragma unroll 1   // one step is 256 FMAs per lane; unrolling further only thrashes the instruction cache
-                for (int it = 0; it < KT / 128; ++it) {
-                    const int kl = it * 128 + 4 * lane;       // offset inside the tile
-                    const int base = kt * KT + kl;            // offset inside the row
-                    // this step's values (normalised if asked for) leave v_next before the next fetch overwrites it
-                    float xs[TPW][4];
+            cp_async_wait<1>();          // this thread's copies of `stage` have landed
+            if (use_ln) normalise(stage);
+            __syncthreads();             // ... and everybody else's
+            const int buf = stage & 1;
 #pragma unroll
-                    for (int i = 0; i < TPW; ++i) {
-                        const float4 v = v_next[i];
-                        if (use_ln) {
-                            xs[i][0] = ln_apply(v.x, mean[i], rstd[i], g_next.x);
-                            xs[i][1] = ln_apply(v.y, mean[i], rstd[i], g_next.y);
-                            xs[i][2] = ln_apply(v.z, mean[i], rstd[i], g_next.z);
-                            xs[i][3] = ln_apply(v.w, mean[i], rstd[i], g_next.w);
-                        } else {
-                            xs[i][0] = v.x; xs[i][1] = v.y; xs[i][2] = v.z; xs[i][3] = v.w;
-                        }
-                    }
-                    fetch(base + 128 < ntiles * KT ? base + 128 : 4 * lane);
-                    if (base < D) {
-                        // Positions past the end of a row (D not a multiple of 4) hold zeros in the centroid tile and
-                        // a zero gamma or zero x: their products are exact zeros and leave the partial sums'
-                        // bits unchanged, so they need no predicate.
+            for (int step = 0; step < RT_STEPS; ++step) {
+                if (stage * RT_STAGE_FLOATS + step * 128 >= D) break;
+                const float4* xt = xs + (buf * RT_STEPS + step) * 1024;
+                const float4* ct = cs + (buf * RT_STEPS + step) * 1024;
+                float4 c[8];
 #pragma unroll
-                        for (int j = 0; j < EG; ++j) {
-                            const float4 c = *reinterpret_cast<const float4*>(tile + j * KT + kl);
-                            const float cc[4] = {c.x, c.y, c.z, c.w};
+                for (int jj = 0; jj < 8; ++jj) {
+                    const int row = te + 4 * jj;
+                    c[jj] = ct[row * 32 + rt_slot(l, row)];
+                }
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) {
+                for (int j = 0; j < 8; ++j) {
+                    const int row = tt + 4 * j;
+                    const float4 x = xt[row * 32 + rt_slot(l, row)];
+                    // Elements past the end of a row are zero in both tiles: their products are exact zeros and
+                    // leave the partial sums' bits unchanged, so they need no predicate.
 #pragma unroll
-                                for (int i = 0; i < TPW; ++i) acc[i][j] = __fmaf_rn(xs[i][k], cc[k], acc[i][j]);
-                            }
-                        }
-                    }
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.x, c[jj].x, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.y, c[jj].y, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.z, c[jj].z, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.w, c[jj].w, acc[j][jj]);
                 }
             }
-            __syncthreads();   // everyone is done with tile kt before it is overwritten
+            __syncthreads();             // everyone is done with this stage's tiles before they are refilled
         }
+
+        // butterfly, first step (xor 16 over l): the two halves of the warp hold l and l + 16 of the same pairs
 #pragma unroll
-        for (int j = 0; j < EG; ++j) {
-            if (e0 + j < E) {
+        for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int i = 0; i < TPW; ++i) {
-                    const float s = warp_xor_sum(acc[i][j]);
-                    if (s > best[i]) {  // strict '>': the first maximum wins (plugin/cuda/moe.cu:62-67)
-                        best[i] = s;
-                        best_e[i] = e0 + j;
-                    }
-                }
-            }
-        }
-    }
-    if (HALVES > 1) {
-        // merge the halves' winners: highest score, lowest expert index among equal scores -- the expert the
-        // reference's sequential strict '>' scan would have kept
-        if (half == 1 && lane == 0) {
+            for (int jj = 0; jj < 8; ++jj)
+                acc[j][jj] = __fadd_rn(acc[j][jj], __shfl_xor_sync(0xffffffffu, acc[j][jj], 16));
+        if (lane < 16) {
 #pragma unroll
-            for (int i = 0; i < TPW; ++i) {
-                s_merge_score[warp][i] = best[i];
-                s_merge_e[warp][i] = best_e[i];
-            }
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj)
+                    red[(warp * RT_TOKENS + tt + 4 * j) * RT_RED_PITCH + te + 4 * jj] = acc[j][jj];
         }
         __syncthreads();
-        if (half == 0) {
+        // steps xor 8, 4, 2, 1 and the argmax: warp -> tokens warp and warp + 16, lane -> expert e0 + lane
 #pragma unroll
-            for (int i = 0; i < TPW; ++i) {
-                const float so = s_merge_score[warp][i];
-                const int eo = s_merge_e[warp][i];
-                if (eo >= 0 && (best_e[i] < 0 || so > best[i] || (so == best[i] && eo < best_e[i]))) {
-                    best[i] = so;
-                    best_e[i] = eo;
+        for (int q = 0; q < 2; ++q) {
+            const int t = warp + 16 * q;
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = red[(i * RT_TOKENS + t) * RT_RED_PITCH + lane];
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1)
+#pragma unroll
+                for (int i = 0; i < off; ++i) v[i] = __fadd_rn(v[i], v[i + off]);
+            // Candidates of this pass have higher indices than the running winner, so they replace it only when
+            // strictly greater; among themselves the lowest index wins a tie.  That is the expert the reference's
+            // sequential strict '>' scan keeps (plugin/cuda/moe.cu:62-67).  A NaN score is never greater.
+            float cand = v[0];
+            int cand_e = (e0 + lane < E && cand > best[q]) ? e0 + lane : -1;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                const float os = __shfl_xor_sync(0xffffffffu, cand, off);
+                const int oe = __shfl_xor_sync(0xffffffffu, cand_e, off);
+                if (oe >= 0 && (cand_e < 0 || os > cand || (os == cand && oe < cand_e))) {
+                    cand = os;
+                    cand_e = oe;
                 }
             }
+            if (cand_e >= 0) {
+                best[q] = cand;
+                best_e[q] = cand_e;
+            }
         }
+        __syncthreads();   // the partial sums have been read before the next pass refills the tiles
     }
-    if (lane == 0 && warp_live && half == 0) {
+    if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < TPW; ++i) {
-            if (!live[i]) continue;
-            gate[t0 + i] = best_e[i];
-            if (score) score[t0 + i] = best[i];
-            if (best_e[i] < 0 && status) atomicOr(status, STATUS_NO_EXPERT);
+        for (int q = 0; q < 2; ++q) {
+            const long long t = t0 + warp + 16 * q;
+            if (t >= T) continue;
+            gate[t] = best_e[q];
+            if (score) score[t] = best[q];
+            if (best_e[q] < 0 && status) atomicOr(status, STATUS_NO_EXPERT);
         }
     }
 }
@@ -279,45 +289,14 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
     }
     if (T == 0) return INFMOE_OK;
     const bool vec = (D % 4 == 0) && (((uintptr_t)X | (uintptr_t)C | (uintptr_t)gamma) % 16 == 0);
-    constexpr int TPW = 4, EG = 16, KT = 512;
-    constexpr int SMEM = 2 * EG * KT * (int)sizeof(float);
-    // The kernel is bound by FP32 FMAs, so a CTA's time grows with its warps and the launch takes
-    // waves x warps: pick the warp count (5..8) that wastes the least of the last wave.
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        INFMOE_CUDA_TRY(cudaGetDevice(&dev));
-        INFMOE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long grid = (T + RT_TOKENS - 1) / RT_TOKENS;
+    if (vec) {
+        INFMOE_CUDA_TRY(cudaFuncSetAttribute(route_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
+        route_kernel<true><<<(unsigned)grid, RT_THREADS, RT_SMEM, stream>>>(X, C, gamma, T, D, E, gate, score, status);
+    } else {
+        INFMOE_CUDA_TRY(cudaFuncSetAttribute(route_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
+        route_kernel<false><<<(unsigned)grid, RT_THREADS, RT_SMEM, stream>>>(X, C, gamma, T, D, E, gate, score, status);
     }
-    const int halves = E > EG / 2 ? 2 : 1;
-    int warps = 7;
-    long long best_cost = -1;
-    for (int w = (halves == 2 ? 7 : 8); w >= 5; --w) {
-        const long long ctas = (T + (long long)w * TPW - 1) / ((long long)w * TPW);
-        const long long cost = ((ctas + sms - 1) / sms) * w;
-        if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            warps = w;
-        }
-    }
-    const long long grid = (T + (long long)warps * TPW - 1) / ((long long)warps * TPW);
-#define INFMOE_ROUTE_LAUNCH(W, H)                                                                                  \
-    do {                                                                                                           \
-        /* two halves: 8 experts per group and half, so that the accumulators of 448 threads fit the register file */ \
-        auto kern = route_kernel<TPW, EG / H, KT, W, H>;                                                           \
-        INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));            \
-        kern<<<(unsigned)grid, W * H * 32, SMEM, stream>>>(X, C, gamma, T, D, E, vec ? 1 : 0, gate, score, status); \
-    } while (0)
-    switch (warps * 10 + halves) {
-        case 51: INFMOE_ROUTE_LAUNCH(5, 1); break;
-        case 61: INFMOE_ROUTE_LAUNCH(6, 1); break;
-        case 71: INFMOE_ROUTE_LAUNCH(7, 1); break;
-        case 81: INFMOE_ROUTE_LAUNCH(8, 1); break;
-        case 52: INFMOE_ROUTE_LAUNCH(5, 2); break;
-        case 62: INFMOE_ROUTE_LAUNCH(6, 2); break;
-        default: INFMOE_ROUTE_LAUNCH(7, 2); break;
-    }
-#undef INFMOE_ROUTE_LAUNCH
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;

@@ -40,21 +40,25 @@ scatter_kernel(long long T, int D, int vec, const float* __restrict__ X, const f
     if (lane == 0 && coeff && rcoeff) rcoeff[j] = coeff[p];
 }
 
-// The layer's fused scatter: one read of X[pos[j],:] produces the routed row,
-// its per-expert LayerNorm h = LN(x; gamma_e) (T5FFLayer.cc:99-103) already
-// split for the grouped GEMM, and the routed score.  gamma is [E][D]; the
-// expert of row j is gate[pos[j]].  PACK = false: TF32 head and FP32 tail
-// planes h_hi / h_lo [T][D] (exact split, CUDA-core GEMM); PACK = true: head
-// plane h_hi and the packed BF16 plane (see store_pack4) in h_lo (tensor-core GEMM).
+// The layer's fused scatter: one read of X[pos[j],:] produces its per-expert
+// LayerNorm h = LN(x; gamma_e) (T5FFLayer.cc:99-103) already split for the
+// grouped GEMM, the routed score and, when `routed` is given, the routed row
+// itself (the tensor-core GEMM reads its residual from X through pos[] and needs
+// no such copy).  gamma is [E][D]; the expert of row j is gate[pos[j]].  Rows at or
+// past *valid_rows (tokens without an expert, empty receive slots) are skipped.
+// PACK = false: TF32 head and FP32 tail planes h_hi / h_lo [T][D] (exact split,
+// CUDA-core GEMM); PACK = true: head plane h_hi and the packed BF16 plane (see
+// store_pack4) in h_lo (tensor-core GEMM).
 template <bool PACK>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X, const float* __restrict__ score,
                         const int* __restrict__ pos, const int* __restrict__ gate,
-                        const float* __restrict__ gamma_all, float* __restrict__ routed,
-                        float* __restrict__ rscore, float* __restrict__ h_hi, float* __restrict__ h_lo) {
+                        const float* __restrict__ gamma_all, const int* __restrict__ valid_rows,
+                        float* __restrict__ routed, float* __restrict__ rscore, float* __restrict__ h_hi,
+                        float* __restrict__ h_lo) {
     const int lane = threadIdx.x & 31;
     const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-    if (j >= T) return;
+    if (j >= T || (valid_rows && j >= *valid_rows)) return;
     const int p = pos[j];
     const int e = gate[p];
     const float* src = X + (long long)p * D;
@@ -90,13 +94,81 @@ scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X
     if (lane == 0 && rscore && score) rscore[j] = score[p];
 }
 
-// out[pos[j],:] = in[j,:]
+// The same for aligned rows of up to 128 * NV floats, with more bytes in flight per warp: the whole row is
+// fetched into registers by back-to-back 128-bit loads (NV per lane) before any of it is used, so it crosses HBM
+// once in one burst and both statistics passes and the split run from registers.  The additions happen in the
+// order of warp_row_stats, so the results are the same bits.  Few rows per SM (4096 rows on 148 SMs) would
+// otherwise leave the memory system half idle.
+template <bool PACK, int NV>
+__global__ void __launch_bounds__(128)
+scatter_ln_split_reg_kernel(long long T, int D, const float* __restrict__ X, const float* __restrict__ score,
+                            const int* __restrict__ pos, const int* __restrict__ gate,
+                            const float* __restrict__ gamma_all, const int* __restrict__ valid_rows,
+                            float* __restrict__ routed, float* __restrict__ rscore, float* __restrict__ h_hi,
+                            float* __restrict__ h_lo) {
+    const int lane = threadIdx.x & 31;
+    const long long j = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (j >= T || (valid_rows && j >= *valid_rows)) return;
+    const int p = pos[j];
+    const int e = gate[p];
+    const float4* src = reinterpret_cast<const float4*>(X + (long long)p * D);
+    const float4* gamma = reinterpret_cast<const float4*>(gamma_all + (long long)e * D);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int base = 4 * lane + 128 * i;
+        v[i] = base < D ? src[base >> 2] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (4 * lane + 128 * i < D) s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, v[i].x), v[i].y), v[i].z), v[i].w);
+    const float mean = __fdiv_rn(warp_xor_sum(s), (float)D);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (4 * lane + 128 * i < D) {
+            float d = __fsub_rn(v[i].x, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v[i].y, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v[i].z, mean);
+            q = __fmaf_rn(d, d, q);
+            d = __fsub_rn(v[i].w, mean);
+            q = __fmaf_rn(d, d, q);
+        }
+    const float var = __fdiv_rn(warp_xor_sum(q), (float)D);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-6f)));
+    uint16_t* pack_row = PACK ? reinterpret_cast<uint16_t*>(h_lo) + j * (long long)pack_pitch(D) : nullptr;
+    const int k_end = PACK ? ((D + 31) & ~31) : D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int base = 4 * lane + 128 * i;
+        if (base >= k_end) continue;
+        float hh[4] = {0.f, 0.f, 0.f, 0.f}, ll[4] = {0.f, 0.f, 0.f, 0.f};
+        if (base < D) {
+            const float4 g = gamma[base >> 2];
+            split_tf32(ln_apply(v[i].x, mean, rstd, g.x), hh[0], ll[0]);
+            split_tf32(ln_apply(v[i].y, mean, rstd, g.y), hh[1], ll[1]);
+            split_tf32(ln_apply(v[i].z, mean, rstd, g.z), hh[2], ll[2]);
+            split_tf32(ln_apply(v[i].w, mean, rstd, g.w), hh[3], ll[3]);
+            const long long o = j * D + base;
+            if (routed) *reinterpret_cast<float4*>(routed + o) = v[i];
+            *reinterpret_cast<float4*>(h_hi + o) = make_float4(hh[0], hh[1], hh[2], hh[3]);
+            if (!PACK) *reinterpret_cast<float4*>(h_lo + o) = make_float4(ll[0], ll[1], ll[2], ll[3]);
+        }
+        if (PACK) store_pack4(pack_row, base, hh, ll);
+    }
+    if (lane == 0 && rscore && score) rscore[j] = score[p];
+}
+
+// out[pos[j],:] = in[j,:] for the rows below *valid_rows (all rows when valid_rows is NULL)
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 gather_kernel(long long T, int D, int vec, const float* __restrict__ in, const int* __restrict__ pos,
-              float* __restrict__ out) {
+              const int* __restrict__ valid_rows, float* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-    if (j >= T) return;
+    if (j >= T || (valid_rows && j >= *valid_rows)) return;
     copy_row(in + j * D, out + (long long)pos[j] * D, D, vec != 0, lane);
 }
 
@@ -104,10 +176,11 @@ gather_kernel(long long T, int D, int vec, const float* __restrict__ in, const i
 // (sigmoid: plugin/cuda/common.cuh:24-27)
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 mix_gather_kernel(long long T, int D, int vec, const int* __restrict__ pos, const float* __restrict__ routed,
-                  const float* __restrict__ post, const float* __restrict__ coeff, float* __restrict__ out) {
+                  const float* __restrict__ post, const float* __restrict__ coeff,
+                  const int* __restrict__ valid_rows, float* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const long long j = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-    if (j >= T) return;
+    if (j >= T || (valid_rows && j >= *valid_rows)) return;
     const float alpha = mix_alpha(coeff[j]);
     const float beta = 1.0f - alpha;
     const float* a = post + j * D;
@@ -246,17 +319,32 @@ int launch_scatter(long long T, int D, const float* X, const float* coeff, const
 }
 
 int launch_scatter_ln_split(long long T, int D, const float* X, const float* score, const int* pos, const int* gate,
-                            const float* gamma_all, float* routed, float* rscore, float* h_hi, float* h_lo, bool pack,
-                            cudaStream_t stream) {
+                            const float* gamma_all, const int* valid_rows, float* routed, float* rscore, float* h_hi,
+                            float* h_lo, bool pack, cudaStream_t stream) {
     if (T == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(X) && aligned16(routed) && aligned16(h_hi) && aligned16(h_lo) &&
                     aligned16(gamma_all);
-    if (pack)
-        scatter_ln_split_kernel<true><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate,
-                                                                                  gamma_all, routed, rscore, h_hi, h_lo);
+    if (vec && D <= 4096) {
+        const unsigned grid = (unsigned)((T + 3) / 4);
+#define INFMOE_SCATTER_REG(PACK, NV)                                                                               \
+    scatter_ln_split_reg_kernel<PACK, NV><<<grid, 128, 0, stream>>>(T, D, X, score, pos, gate, gamma_all, valid_rows, \
+                                                                    routed, rscore, h_hi, h_lo)
+        if (pack) {
+            if (D <= 1024) INFMOE_SCATTER_REG(true, 8);
+            else if (D <= 2048) INFMOE_SCATTER_REG(true, 16);
+            else INFMOE_SCATTER_REG(true, 32);
+        } else {
+            if (D <= 1024) INFMOE_SCATTER_REG(false, 8);
+            else if (D <= 2048) INFMOE_SCATTER_REG(false, 16);
+            else INFMOE_SCATTER_REG(false, 32);
+        }
+#undef INFMOE_SCATTER_REG
+    } else if (pack)
+        scatter_ln_split_kernel<true><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(
+            T, D, vec, X, score, pos, gate, gamma_all, valid_rows, routed, rscore, h_hi, h_lo);
     else
-        scatter_ln_split_kernel<false><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, X, score, pos, gate,
-                                                                                   gamma_all, routed, rscore, h_hi, h_lo);
+        scatter_ln_split_kernel<false><<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(
+            T, D, vec, X, score, pos, gate, gamma_all, valid_rows, routed, rscore, h_hi, h_lo);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -292,28 +380,30 @@ int launch_rows_to_ptrs(long long n, int D, const float* in, const unsigned long
     return INFMOE_OK;
 }
 
-int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream) {
+int launch_gather(long long T, int D, const float* in, const int* pos, float* out, cudaStream_t stream,
+                  const int* valid_rows) {
     if (T < 0 || D <= 0 || !in || !pos || !out) {
         set_error("expert_gather: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     if (T == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(in) && aligned16(out);
-    gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, in, pos, out);
+    gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, in, pos, valid_rows, out);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
 }
 
 int launch_mix_gather(long long T, int D, const int* pos, const float* routed, const float* post,
-                      const float* coeff, float* out, cudaStream_t stream) {
+                      const float* coeff, float* out, cudaStream_t stream, const int* valid_rows) {
     if (T < 0 || D <= 0 || !pos || !routed || !post || !coeff || !out) {
         set_error("expert_mix_gather: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
     if (T == 0) return INFMOE_OK;
     const int vec = (D % 4 == 0) && aligned16(routed) && aligned16(post) && aligned16(out);
-    mix_gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, pos, routed, post, coeff, out);
+    mix_gather_kernel<<<row_grid(T), ROW_WARPS * 32, 0, stream>>>(T, D, vec, pos, routed, post, coeff, valid_rows,
+                                                                  out);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;
@@ -362,6 +452,17 @@ int launch_gelu_dot(const float* a, float* b, size_t len, cudaStream_t stream) {
     if (len == 0) return INFMOE_OK;
     const unsigned grid = (unsigned)((len + 255) / 256 < 148 * 16 ? (len + 255) / 256 : 148 * 16);
     gelu_dot_kernel<<<grid, 256, 0, stream>>>(a, b, len);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    return INFMOE_OK;
+}
+
+namespace {
+__global__ void fill_int_kernel(int* dst, int value) { *dst = value; }
+}  // namespace
+
+int launch_fill_int(int* dst, int value, cudaStream_t stream) {
+    fill_int_kernel<<<1, 1, 0, stream>>>(dst, value);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     return INFMOE_OK;

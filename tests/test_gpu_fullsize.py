@@ -83,6 +83,95 @@ def test_base_layer_zipf_full_size(oracle):
     assert count.max() > 10 * np.median(count)            # the skew is real: a few experts take most tokens
 
 
+def test_offload_decode_full_size(oracle):
+    """The decode regime at its real size (E=32, d_model=4096, d_ff=10240, 64 tokens): experts streamed from pinned
+    host memory through max_concurrency = 2 slots, and through the layer's expert cache (cold, then warm), give the
+    bits of the resident layer; sampled rows agree with the FP64 oracle."""
+    import torch
+    from infmoe_b200 import MoELayer, synth
+    assert torch.cuda.is_available()
+    dev = torch.device("cuda")
+    w = synth.WORKLOADS["offload_t64"]
+    x, c, ln = synth.gen_inputs(w)
+    E, D, F = w.expert_count, w.embedding_size, w.hidden_size
+    resident = MoELayer.create(E, D, F, 2, c, None, "T5_FF", w.variant, ln)
+    streamed = MoELayer.create(E, D, F, 2, c, None, "T5_FF", w.variant, ln)
+    for e in range(E):
+        ws = synth.gen_expert_torch(w, e, dev)
+        resident.set_expert(e, *ws)
+        streamed.set_expert(e, *[t.cpu().numpy() for t in ws])
+    resident.set_residency(1)
+    streamed.set_residency(0)
+    cached = streamed.clone()               # shares the pinned host weights
+    cached.set_residency(0)
+    cached.set_expert_cache(E)
+    want = resident.forward_host(x)
+    assert np.isfinite(want).all()
+    ogate, oscore = oracle.route(x, c, ln)
+    active = np.unique(ogate)
+    assert active.size > 20                 # most experts are hit: the slots are recycled many times
+    np.testing.assert_array_equal(streamed.forward_host(x), want)
+    copied = streamed.weight_h2d_bytes()
+    assert copied == active.size * 12 * D * F
+    np.testing.assert_array_equal(cached.forward_host(x), want)          # cold: every active expert is copied once
+    cold = cached.weight_h2d_bytes()
+    assert cold == active.size * 12 * D * F
+    np.testing.assert_array_equal(cached.forward_host(x), want)          # warm: nothing is copied
+    assert cached.weight_h2d_bytes() == cold
+    rng = np.random.default_rng(1)
+    for t in rng.choice(w.tokens, size=3, replace=False):
+        e = int(ogate[t])
+        ex = [a.cpu().numpy() for a in synth.gen_expert_torch(w, e, dev)]
+        y64 = oracle.expert_ffn_f64(x[t:t + 1], *ex)
+        assert oracle.rel_l2(want[t:t + 1], y64) <= TOL
+    for layer in (cached, streamed, resident):
+        layer.terminate()
+
+
+@pytest.mark.parametrize("case", ["row_scales", "outliers", "large_magnitude"])
+def test_split_operand_products_with_wide_value_ranges(oracle, case):
+    """The expert GEMMs add two BF16 correction products to a TF32 head product.  Inputs drawn from N(0, 1) never
+    test what 8-bit correction operands do to weights with a wide exponent spread, with outliers, or to the
+    integer TF32 rounding at large magnitudes (where a mantissa carry moves the exponent): these cases do."""
+    import torch
+    assert torch.cuda.is_available()
+    from tests import gpu_util as g
+    rng = np.random.default_rng({"row_scales": 11, "outliers": 12, "large_magnitude": 13}[case])
+    n, D, F = 150, 512, 1024
+    x = rng.standard_normal((n, D)).astype(np.float32)
+    ln = (1 + 0.01 * rng.standard_normal(D)).astype(np.float32)
+    wi0 = (rng.standard_normal((F, D)) / np.sqrt(D)).astype(np.float32)
+    wi1 = (rng.standard_normal((F, D)) / np.sqrt(D)).astype(np.float32)
+    wo = (rng.standard_normal((D, F)) / np.sqrt(F)).astype(np.float32)
+    if case == "row_scales":
+        # every weight row (and column of wo) at its own scale, 2^-12 .. 2^12
+        wi0 *= np.exp2(rng.uniform(-12, 12, size=(F, 1))).astype(np.float32)
+        wi1 *= np.exp2(rng.uniform(-12, 12, size=(F, 1))).astype(np.float32)
+        wo *= np.exp2(rng.uniform(-12, 12, size=(1, F))).astype(np.float32) * np.float32(2.0 ** -12)
+        x *= np.exp2(rng.uniform(-8, 8, size=(n, 1))).astype(np.float32)
+    elif case == "outliers":
+        for m in (wi0, wi1, wo):
+            idx = rng.random(m.shape) < 1e-3
+            m[idx] *= np.float32(1000.0)
+        x[rng.random(x.shape) < 1e-3] *= np.float32(300.0)
+    else:
+        # weights near 2^60, LayerNorm weight 2^-60: values whose TF32 rounding carries into the exponent included
+        ln = (ln * np.float32(2.0 ** -60)).astype(np.float32)
+        wi0 = (wi0 * np.float32(2.0 ** 60)).astype(np.float32)
+        wi1 = (wi1 * np.float32(2.0 ** 60)).astype(np.float32)
+        scale = np.float32(2.0 ** 60 / np.sqrt(D))
+        wi0[::7, ::5] = scale * np.float32(np.nextafter(np.float32(2.0), np.float32(0.0)))
+        wi1[::3, ::11] = -scale * np.float32(np.nextafter(np.float32(0.5), np.float32(0.0)))
+    got = g.t5ff_run(x, ln, wi0, wi1, wo)
+    y64 = oracle.expert_ffn_f64(x, ln, wi0, wi1, wo)
+    assert np.isfinite(got).all()
+    err = oracle.rel_l2(got, y64)
+    err_ffn = oracle.rel_l2(got - x, y64 - x)
+    f32 = oracle.rel_l2(oracle.expert_ffn_f32(x, ln, wi0, wi1, wo), y64)
+    print(f"{case}: rel L2 {err:.2e}, FFN term alone {err_ffn:.2e}, plain FP32 evaluation {f32:.2e}")
+    assert err <= TOL, err
+
+
 def test_identity_full_size_roundtrip():
     """Scatter then gather over 65536 x 4096 floats is the identity (the Identity sublayer)."""
     import torch

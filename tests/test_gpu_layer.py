@@ -253,6 +253,88 @@ def test_nan_input_is_reported_not_trapped(torch_cuda):
     layer.terminate()
 
 
+@pytest.mark.parametrize("variant", ["cpm_2", "base_layer"])
+def test_nan_tokens_touch_nothing_outside_their_own_rows(torch_cuda, oracle, variant):
+    """A workspace is not zeroed between calls (TensorRT hands out the same block again and again).  With a few
+    NaN rows in the input the call must report them, leave their output rows alone, and still give every other
+    token its expert's result: no stage may index anything with what a previous call left in the workspace."""
+    from infmoe_b200 import capi, synth
+    torch = torch_cuda
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=6, embedding_size=128, hidden_size=256,
+                     batch=1, seq_len=500)
+    layer, x, c, ln, experts = _build(w, synth, from_npz=False)
+    layer.set_residency(1)
+    T, D = w.tokens, w.embedding_size
+    need = layer.get_workspace_size(T)
+    ws = torch.full((need,), 0x7f, dtype=torch.uint8, device="cuda")      # garbage indices everywhere
+    bad_rows = np.array([0, 17, 255, 256, 499])
+    bad = x.copy()
+    bad[bad_rows, 5] = np.nan
+    dx = torch.from_numpy(bad).cuda()
+    out = torch.full((T, D), -7.0, device="cuda")
+    layer.enqueue(dx.data_ptr(), out.data_ptr(), ws.data_ptr(), need, T, torch.cuda.current_stream().cuda_stream)
+    with pytest.raises(capi.InfMoEError) as e:
+        layer.sync_status(torch.cuda.current_stream().cuda_stream)
+    assert e.value.status == 3
+    got = out.cpu().numpy()
+    assert np.all(got[bad_rows] == -7.0)                                  # untouched
+    good = np.setdiff1d(np.arange(T), bad_rows)
+    ref = oracle.layer_forward_f32(x[good], w.variant, c, ln, experts)
+    o64 = oracle.layer_forward_f64(x[good], w.variant, ref["gate"], ref["score"], experts)
+    assert oracle.rel_l2(got[good], o64) <= TOL
+    gate, _, pos, count, offset = _routing(layer, T, w.expert_count, torch)
+    assert np.all(gate[bad_rows] == -1) and offset[-1] == T - bad_rows.size
+    np.testing.assert_array_equal(pos[offset[-1]:], bad_rows)
+    layer.terminate()
+
+
+@pytest.mark.parametrize("variant", ["cpm_2", "base_layer"])
+def test_deserialised_layer_gives_the_same_bits(torch_cuda, oracle, tmp_path, variant):
+    """serialize -> deserialize -> initialize -> enqueue (the deserialising constructor of the reference,
+    plugin/MoELayerPlugin.cc:104-143, fed by serialize, :425-458) equals the layer the blob came from."""
+    from infmoe_b200 import MoELayer, synth
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=6, embedding_size=128, hidden_size=256,
+                     batch=2, seq_len=150)
+    layer, x, c, ln, experts = _build(w, synth, tmp_path)
+    want = _check(layer, w, x, c, ln, experts, oracle, torch_cuda)
+    blob = layer.serialize()
+    layer.terminate()
+    twin = MoELayer.deserialize(blob)
+    assert twin.moe_variant == variant and twin.expert_count == 6
+    twin.initialize()                       # reads the weight file named in the blob
+    got = _check(twin, w, x, c, ln, experts, oracle, torch_cuda)
+    np.testing.assert_array_equal(got, want)
+    clone = twin.clone()                    # TensorRT runs clones of the deserialised plugin
+    np.testing.assert_array_equal(clone.forward_host(x), want)
+    clone.terminate()
+    twin.terminate()
+
+
+def test_clones_on_two_streams_share_one_upload(torch_cuda, oracle, tmp_path):
+    """Clones share the expert store; TensorRT gives each execution context its own clone and stream.  The first
+    enqueue uploads the weights on its stream; a clone whose first enqueue overlaps it on another stream must
+    wait for that upload instead of reading half-written planes."""
+    from infmoe_b200 import synth
+    torch = torch_cuda
+    w = synth.scaled(synth.WORKLOADS["cpm2"], expert_count=8, embedding_size=512, hidden_size=2048, batch=1,
+                     seq_len=400)
+    layer, x, c, ln, experts = _build(w, synth, tmp_path, residency=1)
+    clone = layer.clone()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    dx = torch.from_numpy(x).cuda()
+    o1, o2 = torch.empty_like(dx), torch.empty_like(dx)
+    torch.cuda.synchronize()
+    layer.forward(dx, o1, stream=s1.cuda_stream)      # queues 8 x (3 copies + 2 retile kernels) and returns at once
+    clone.forward(dx, o2, stream=s2.cuda_stream)      # sees the experts marked resident
+    torch.cuda.synchronize()
+    ref = oracle.layer_forward_f32(x, w.variant, c, ln, experts)
+    o64 = oracle.layer_forward_f64(x, w.variant, ref["gate"], ref["score"], experts)
+    assert oracle.rel_l2(o1.cpu().numpy(), o64) <= TOL
+    assert torch.equal(o1, o2)
+    clone.terminate()
+    layer.terminate()
+
+
 def test_enqueue_argument_checks(torch_cuda):
     from infmoe_b200 import MoELayer, capi, synth
     torch = torch_cuda

@@ -114,6 +114,38 @@ def test_dispatch_all_to_one_and_bad_gate(g, oracle):
     assert status & 2
 
 
+@pytest.mark.parametrize("T,E,bad_every", [(10, 3, 2), (2500, 6, 7), (9000, 40, 3), (70001, 130, 1000)])
+def test_dispatch_defines_everything_when_gates_are_invalid(g, T, E, bad_every):
+    """Tokens without an expert (gate -1 from a NaN row, or any index outside [0, E)) must not leave a hole in
+    what dispatch hands on: pos[] stays a permutation, the valid tokens keep the reference's stable order, the
+    others follow in ascending order, offset[E] counts the valid ones, and the status word says so."""
+    import torch
+    from infmoe_b200 import capi
+    rng = np.random.default_rng(T)
+    gate = rng.integers(0, E, size=T).astype(np.int32)
+    bad = np.arange(0, T, bad_every)
+    gate[bad] = np.where(np.arange(bad.size) % 2 == 0, -1, E + 5)
+    dg = g.dev(gate)
+    SENTINEL = -123456
+    pos = torch.full((T,), SENTINEL, dtype=torch.int32, device="cuda")     # what a reused workspace looks like
+    count = torch.full((E,), SENTINEL, dtype=torch.int32, device="cuda")
+    offset = torch.full((E + 1,), SENTINEL, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    capi.check(capi.lib().infmoe_expert_count(T, E, dg.data_ptr(), pos.data_ptr(), count.data_ptr(),
+                                              offset.data_ptr(), status.data_ptr(), g.stream()))
+    torch.cuda.synchronize()
+    pos, count, offset = pos.cpu().numpy(), count.cpu().numpy(), offset.cpu().numpy()
+    valid = (gate >= 0) & (gate < E)
+    assert int(status.item()) & 2
+    assert not np.any(pos == SENTINEL)
+    np.testing.assert_array_equal(np.sort(pos), np.arange(T))
+    assert offset[E] == valid.sum()
+    np.testing.assert_array_equal(count, np.bincount(gate[valid], minlength=E))
+    np.testing.assert_array_equal(offset[:E], np.concatenate(([0], np.cumsum(count)[:-1])))
+    order = np.argsort(np.where(valid, gate, E), kind="stable")       # stable: ascending token index per bucket
+    np.testing.assert_array_equal(pos, order)
+
+
 @pytest.mark.parametrize("T,D", [(1, 4), (50, 12), (33, 130), (512, 1024), (100, 4096)])
 def test_scatter_gather_mix(g, oracle, T, D):
     import torch

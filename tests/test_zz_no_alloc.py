@@ -1,9 +1,9 @@
 """The allocation-free expert FFN entry point, infmoe_t5ff_run_static.
 
 Some callers of this library cannot allocate device memory at the moment they need the
-expert FFN: a TensorRT plugin inside enqueue(), code under CUDA-graph capture, a serving loop
-that must not trigger cudaMalloc's device-wide synchronisation.  For them the library carries
-its own scratch array.  These tests call the entry point through the C ABI and compare it with
+expert FFN: a TensorRT plugin inside enqueue(), whose engine fixed its memory plan when it was
+built, and a serving loop that must not trigger cudaMalloc's device-wide synchronisation.  For
+them the library carries its own scratch array.  These tests call the entry point through the C ABI and compare it with
 infmoe_t5ff_run (which takes a caller-allocated workspace) on two calls in a row; since both
 run the same kernels on the same inputs the outputs must agree to the last bit, which is well
 inside the 1e-5 relative-L2 tolerance used for this path elsewhere.
@@ -57,6 +57,32 @@ def test_static_scratch_matches_workspace_version_twice_in_a_row(oracle):
         assert oracle.rel_l2(got, want) <= TOL
         np.testing.assert_array_equal(got, want)
         assert oracle.rel_l2(got, oracle.expert_ffn_f64(x, ln, wi0, wi1, wo)) <= TOL
+
+
+def test_static_scratch_calls_allocate_nothing():
+    """Free device memory is the same before and after the second and third call (the first call may load the
+    module and look up the array's address)."""
+    import torch
+    assert torch.cuda.is_available(), "this test needs a GPU"
+    from infmoe_b200 import capi
+    from tests import gpu_util as g
+    n, D, F = 64, 256, 512
+    x, ln, wi0, wi1, wo = _case(7, n, D, F)
+    dx, dl, d0, d1, do = g.dev(x), g.dev(ln), g.dev(wi0), g.dev(wi1), g.dev(wo)
+    y = torch.empty_like(dx)
+
+    def call():
+        capi.check(capi.lib().infmoe_t5ff_run_static(n, D, F, dl.data_ptr(), d0.data_ptr(), d1.data_ptr(),
+                                                     do.data_ptr(), dx.data_ptr(), y.data_ptr(), g.stream()))
+
+    call()
+    torch.cuda.synchronize()
+    for _ in range(2):
+        free_before, _total = torch.cuda.mem_get_info()     # cudaMemGetInfo: the driver's view, not torch's cache
+        call()
+        torch.cuda.synchronize()
+        free_after, _total = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)
 
 
 def test_static_scratch_rejects_sizes_beyond_its_array():
