@@ -395,6 +395,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ep-cpm2", action="store_true",
+                    help="N > 1: skip the fixed-size expert-parallel case that is otherwise run after the weak one")
     ap.add_argument("--seq-len", type=int, default=None, help="override the workload's sequence length (tuning)")
     ap.add_argument("--cache-slots", type=int, default=0,
                     help="streamed workloads: experts the layer keeps on the device across calls (0 = none, as the "
@@ -411,7 +413,7 @@ def main():
         run_single(args, w)
     else:
         from infmoe_b200 import ep_bench
-        ep_bench.run(args, w, scaling, METRIC, UNIT, ClockSampler, _peaks, workload_config)
+        ep_bench.run(args, w, scaling, METRIC, UNIT, ClockSampler, _peaks, workload_config, gemm_roofline)
 
 
 def resolve_workload(args):

@@ -190,6 +190,72 @@ INFMOE_API int infmoe_weight_file_check(const char* path, int32_t expert_count, 
 INFMOE_API int infmoe_layer_get_config(const infmoe_layer* layer, infmoe_layer_config* out);
 
 /* ------------------------------------------------------------------------ */
+/* Expert parallelism over the GPUs of one node (one process per GPU)         */
+/* ------------------------------------------------------------------------ */
+/* No counterpart in the reference, which runs on device 0 only
+ * (plugin/MoELayerPlugin.cc:319).  An infmoe_ep object is one rank's share of a
+ * MoE layer whose expert_count experts are sharded over `world` ranks in
+ * contiguous blocks: it routes this rank's tokens over all experts, stores every
+ * row into the receive buffer of the rank that owns its expert (peer stores over
+ * NVLink), runs its own experts on what it received and stores the results into
+ * the output buffers of the ranks the tokens came from.  The only cross-GPU
+ * synchronisation is a two-word NCCL all-reduce before and after the experts.
+ * NCCL (libnccl.so.2) is loaded at run time, only when world > 1. */
+typedef struct infmoe_ep infmoe_ep;
+#define INFMOE_EP_ID_BYTES 128
+
+typedef struct infmoe_ep_config {
+    int32_t rank, world;
+    const void* unique_id;             /* INFMOE_EP_ID_BYTES from infmoe_ep_unique_id on one rank, the same on all */
+    int32_t expert_count;              /* experts of the whole layer; divisible by world */
+    int32_t embedding_size, hidden_size;
+    int64_t max_tokens;                /* most tokens any rank passes to one call (sizes the receive regions) */
+    const float* expert_centroids;     /* host, all experts: [expert_count][embedding_size] */
+    const float* layernorm_weight;     /* host [embedding_size]; required iff moe_variant == "cpm_2" */
+    const char* moe_variant;           /* of the whole layer: "cpm_2", "base_layer" or "default" */
+    infmoe_layer* local_experts;       /* a layer object holding this rank's expert_count / world experts (rank r:
+                                          experts r * E/world ...), any variant; borrowed, must outlive the ep object */
+} infmoe_ep_config;
+
+/* ncclGetUniqueId: call on one rank, hand the bytes to all ranks by any host-side channel. */
+INFMOE_API int infmoe_ep_unique_id(void* h_id);
+/* Collective over all ranks: creates the communicator, allocates the buffers and maps the peers' with CUDA IPC
+ * (peer access between the GPUs is required).  Uses the current device. */
+INFMOE_API int infmoe_ep_create(const infmoe_ep_config* cfg, infmoe_ep** out);
+/* One layer pass for this rank's `tokens` rows (collective, stream ordered, does not block the host).
+ * d_out may be the pointer infmoe_ep_output returns (or NULL): then the result is left in that buffer and no copy
+ * is made.  Device-side findings are returned by infmoe_ep_sync_status. */
+INFMOE_API int infmoe_ep_forward(infmoe_ep* ep, const float* d_x, float* d_out, int64_t tokens, void* stream);
+/* The buffer the other ranks store this rank's results into: [max_tokens][embedding_size], token order; valid
+ * after infmoe_ep_forward until the next one. */
+INFMOE_API int infmoe_ep_output(const infmoe_ep* ep, float** d_out);
+/* Host buffers in and out, copies inside; blocks until the result is there and returns the status. */
+INFMOE_API int infmoe_ep_forward_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_t tokens);
+/* Blocks until `stream` is idle; non-zero when this rank (or, for routing, any rank) raised a device-side status. */
+INFMOE_API int infmoe_ep_sync_status(infmoe_ep* ep, void* stream);
+/* Routing results of this rank's tokens in the last pass (as infmoe_layer_last_routing, expert indices global). */
+INFMOE_API int infmoe_ep_last_routing(const infmoe_ep* ep, const int32_t** d_gate, const float** d_score,
+                                      const int32_t** d_pos, const int32_t** d_count, const int32_t** d_offset);
+/* What this rank received in the last pass: filled slots per source rank [world], and per slot (region s starts at
+ * s * region_size) the local expert index and the token index at the source. */
+INFMOE_API int infmoe_ep_received(const infmoe_ep* ep, const int32_t** d_region_count, const int32_t** d_expert_of_slot,
+                                  const int32_t** d_home_of_slot, int64_t* region_size);
+/* Per-phase device timing (CUDA events on the caller's stream): ms[5] = routing + dispatch + sending rows,
+ * waiting for all ranks' rows, experts (incl. storing results), waiting for all ranks' results, copy-out. */
+INFMOE_API int infmoe_ep_set_profiling(infmoe_ep* ep, int enable);
+INFMOE_API int infmoe_ep_phase_ms(infmoe_ep* ep, float* ms, int32_t* calls);
+INFMOE_API int infmoe_ep_destroy(infmoe_ep* ep);
+
+/* All `world` ranks inside this process on the current device, for tests and single-GPU emulation: the peers'
+ * buffers are each other's allocations and one stream orders what the barriers order between processes.  The caller
+ * drives the phases itself: infmoe_ep_forward_begin on every rank, then infmoe_ep_forward_experts on every rank,
+ * then infmoe_ep_forward_end on every rank, all on one stream.  unique_id is ignored. */
+INFMOE_API int infmoe_ep_create_loopback(const infmoe_ep_config* cfgs, int32_t world, infmoe_ep** outs);
+INFMOE_API int infmoe_ep_forward_begin(infmoe_ep* ep, const float* d_x, int64_t tokens, void* stream);
+INFMOE_API int infmoe_ep_forward_experts(infmoe_ep* ep, void* stream);
+INFMOE_API int infmoe_ep_forward_end(infmoe_ep* ep, float* d_out, void* stream);
+
+/* ------------------------------------------------------------------------ */
 /* Stage entry points = the free functions of plugin/cuda/moe.h and ops.h     */
 /* ------------------------------------------------------------------------ */
 

@@ -23,7 +23,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
                      "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
-CORE_SOURCES = ["route.cu", "dispatch.cu", "rows.cu", "ffn_simt.cu", "ffn_umma.cu", "layer.cu", "npz.cc"]
+CORE_SOURCES = ["route.cu", "dispatch.cu", "rows.cu", "ffn_simt.cu", "ffn_umma.cu", "layer.cu", "ep.cu", "npz.cc"]
 PLUGIN_SOURCES = ["plugin/MoELayerPlugin.cc", "plugin/MoELayerPluginCreator.cc", "plugin/host_driver.cc"]
 
 
@@ -83,7 +83,7 @@ def build(verbose: bool = False) -> str:
         core = list(ex.map(lambda s: _compile(nvcc, s, verbose), CORE_SOURCES))
         plugin_srcs = [s for s in PLUGIN_SOURCES if os.path.exists(os.path.join(CSRC, s))]
         plug = list(ex.map(lambda s: _compile(nvcc, s, verbose), plugin_srcs))
-    _link(nvcc, core, LIB, ["-lz"], verbose)
+    _link(nvcc, core, LIB, ["-lz", "-ldl"], verbose)
     if plug:
         _link(nvcc, plug, PLUGIN_LIB, ["-L", PKG, "-linfmoe_b200", "-Xlinker", "-rpath,$ORIGIN"], verbose)
     return LIB

@@ -47,6 +47,26 @@ class LayerConfig(ctypes.Structure):
     ]
 
 
+class EpConfig(ctypes.Structure):
+    """struct infmoe_ep_config"""
+
+    _fields_ = [
+        ("rank", ctypes.c_int32),
+        ("world", ctypes.c_int32),
+        ("unique_id", ctypes.c_void_p),
+        ("expert_count", ctypes.c_int32),
+        ("embedding_size", ctypes.c_int32),
+        ("hidden_size", ctypes.c_int32),
+        ("max_tokens", ctypes.c_int64),
+        ("expert_centroids", ctypes.POINTER(ctypes.c_float)),
+        ("layernorm_weight", ctypes.POINTER(ctypes.c_float)),
+        ("moe_variant", ctypes.c_char_p),
+        ("local_experts", ctypes.c_void_p),
+    ]
+
+
+EP_ID_BYTES = 128
+
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int32
@@ -91,6 +111,21 @@ SIGNATURES = {
     "infmoe_t5ff_run": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],
     "infmoe_t5ff_static_limit": [_i64, _i32, _i32, ctypes.POINTER(_sz), ctypes.POINTER(_sz)],
     "infmoe_t5ff_run_static": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_ep_unique_id": [_vp],
+    "infmoe_ep_create": [ctypes.POINTER(EpConfig), ctypes.POINTER(_vp)],
+    "infmoe_ep_create_loopback": [ctypes.POINTER(EpConfig), _i32, ctypes.POINTER(_vp)],
+    "infmoe_ep_forward": [_vp, _vp, _vp, _i64, _vp],
+    "infmoe_ep_forward_begin": [_vp, _vp, _i64, _vp],
+    "infmoe_ep_forward_experts": [_vp, _vp],
+    "infmoe_ep_forward_end": [_vp, _vp, _vp],
+    "infmoe_ep_output": [_vp, ctypes.POINTER(_vp)],
+    "infmoe_ep_forward_host": [_vp, _vp, _vp, _i64],
+    "infmoe_ep_sync_status": [_vp, _vp],
+    "infmoe_ep_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,
+    "infmoe_ep_received": [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_i64)],
+    "infmoe_ep_set_profiling": [_vp, ctypes.c_int],
+    "infmoe_ep_phase_ms": [_vp, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i32)],
+    "infmoe_ep_destroy": [_vp],
     "infmoe_last_error": [],
 }
 _RESTYPES = {"infmoe_last_error": ctypes.c_char_p, "infmoe_layer_kernel_launches": ctypes.c_int64}

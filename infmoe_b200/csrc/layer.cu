@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "layer_internal.h"
 #include "npz.h"
 
 namespace infmoe {
@@ -1066,6 +1067,28 @@ int infmoe_layer_expert_forward_scatter(infmoe_layer* L, const float* d_rows, co
     return layer_run(L, d_rows, nullptr, d_ws, ws_bytes, rows, stream_v, d_expert_of_row, d_row_score,
                      reinterpret_cast<const unsigned long long*>(d_row_dst));
 }
+
+}  // extern "C"
+
+namespace infmoe {
+int layer_run_slots(infmoe_layer* L, const float* d_rows, const int32_t* d_expert_of_slot, const float* d_slot_score,
+                    const unsigned long long* d_slot_dst, void* d_ws, size_t ws_bytes, int64_t slots,
+                    const int32_t* d_region_count, int32_t region_size, cudaStream_t stream) {
+    if (slots > 0 && (!d_expert_of_slot || !d_slot_dst || !d_region_count || region_size <= 0)) {
+        set_error("layer_run_slots: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (slots == 0) return INFMOE_OK;
+    if (L && L->F < L->D) {
+        set_error("layer_run_slots: needs d_ff >= d_model");
+        return INFMOE_ERR_UNSUPPORTED;
+    }
+    return layer_run(L, d_rows, nullptr, d_ws, ws_bytes, slots, (void*)stream, d_expert_of_slot, d_slot_score,
+                     d_slot_dst, d_region_count, region_size);
+}
+}  // namespace infmoe
+
+extern "C" {
 
 int infmoe_layer_sync_status(infmoe_layer* L, void* stream_v) {
     if (!L) {

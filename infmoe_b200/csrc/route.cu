@@ -54,6 +54,49 @@ static_assert(16 * RT_TOKENS * RT_RED_PITCH * 4 <= RT_SMEM, "the partial sums re
 
 __device__ __forceinline__ int rt_slot(int l, int row) { return l ^ (row & 3) ^ ((l >> 4) << 2); }
 
+// LayerNorm statistics of two rows at once, each in the order of warp_row_stats (same bits); interleaving the two
+// keeps twice as many loads in flight, which is what bounds this phase.
+template <bool VEC>
+__device__ __forceinline__ void warp_two_row_stats(const float* __restrict__ r0, const float* __restrict__ r1, int D,
+                                                   float (&mean)[2], float (&rstd)[2]) {
+    const int lane = threadIdx.x & 31;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 a = load_row4(r0, base, D, VEC), b = load_row4(r1, base, D, VEC);
+        s0 = __fadd_rn(s0, a.x);
+        s1 = __fadd_rn(s1, b.x);
+        if (VEC || base + 1 < D) { s0 = __fadd_rn(s0, a.y); s1 = __fadd_rn(s1, b.y); }
+        if (VEC || base + 2 < D) { s0 = __fadd_rn(s0, a.z); s1 = __fadd_rn(s1, b.z); }
+        if (VEC || base + 3 < D) { s0 = __fadd_rn(s0, a.w); s1 = __fadd_rn(s1, b.w); }
+    }
+    mean[0] = __fdiv_rn(warp_xor_sum(s0), (float)D);
+    mean[1] = __fdiv_rn(warp_xor_sum(s1), (float)D);
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll 8
+    for (int base = 4 * lane; base < D; base += 128) {
+        const float4 a = load_row4(r0, base, D, VEC), b = load_row4(r1, base, D, VEC);
+        float d = __fsub_rn(a.x, mean[0]);
+        q0 = __fmaf_rn(d, d, q0);
+        d = __fsub_rn(b.x, mean[1]);
+        q1 = __fmaf_rn(d, d, q1);
+        if (VEC || base + 1 < D) {
+            d = __fsub_rn(a.y, mean[0]); q0 = __fmaf_rn(d, d, q0);
+            d = __fsub_rn(b.y, mean[1]); q1 = __fmaf_rn(d, d, q1);
+        }
+        if (VEC || base + 2 < D) {
+            d = __fsub_rn(a.z, mean[0]); q0 = __fmaf_rn(d, d, q0);
+            d = __fsub_rn(b.z, mean[1]); q1 = __fmaf_rn(d, d, q1);
+        }
+        if (VEC || base + 3 < D) {
+            d = __fsub_rn(a.w, mean[0]); q0 = __fmaf_rn(d, d, q0);
+            d = __fsub_rn(b.w, mean[1]); q1 = __fmaf_rn(d, d, q1);
+        }
+    }
+    rstd[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(warp_xor_sum(q0), (float)D), 1e-6f)));
+    rstd[1] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(warp_xor_sum(q1), (float)D), 1e-6f)));
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(RT_THREADS, 1)
 route_kernel(const float* __restrict__ X, const float* __restrict__ C, const float* __restrict__ gamma,
@@ -68,18 +111,16 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
     const long long t0 = (long long)blockIdx.x * RT_TOKENS;
     const bool use_ln = gamma != nullptr;
 
-    // row statistics, two tokens per warp
+    // row statistics, two tokens per warp (rows past the end alias the tile's first row)
     if (use_ln) {
-        for (int q = 0; q < 2; ++q) {
-            const int t = warp + 16 * q;
-            if (t0 + t < T) {
-                float mean, rstd;
-                warp_row_stats(X + (t0 + t) * (long long)D, D, VEC, mean, rstd);
-                if (lane == 0) {
-                    s_mean[t] = mean;
-                    s_rstd[t] = rstd;
-                }
-            }
+        float mean[2], rstd[2];
+        warp_two_row_stats<VEC>(X + (t0 + (t0 + warp < T ? warp : 0)) * (long long)D,
+                                X + (t0 + (t0 + warp + 16 < T ? warp + 16 : 0)) * (long long)D, D, mean, rstd);
+        if (lane == 0) {
+            s_mean[warp] = mean[0];
+            s_rstd[warp] = rstd[0];
+            s_mean[warp + 16] = mean[1];
+            s_rstd[warp + 16] = rstd[1];
         }
     }
     __syncthreads();
@@ -116,11 +157,14 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         }
     };
     // LayerNorm of the token chunks this thread staged, in place; elements past the row stay zero
-    auto normalise = [&](int stage) {
+    auto load_gamma = [&](int stage) -> float4 {
+        const int k = stage * RT_STAGE_FLOATS + st_k;
+        return (use_ln && k < D) ? load_row4(gamma, k, D, VEC) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto normalise = [&](int stage, const float4& g) {
         const int buf = stage & 1;
         const int k = stage * RT_STAGE_FLOATS + st_k;
         if (k >= D) return;
-        const float4 g = load_row4(gamma, k, D, VEC);
         float4* xt = xs + (buf * RT_STEPS + st_step) * 1024;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -150,10 +194,11 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         issue(0, e0);
         cp_async_commit();
         for (int stage = 0; stage < nstages; ++stage) {
+            const float4 g = load_gamma(stage);   // in flight while the copies below are issued and awaited
             if (stage + 1 < nstages) issue(stage + 1, e0);
             cp_async_commit();
             cp_async_wait<1>();          // this thread's copies of `stage` have landed
-            if (use_ln) normalise(stage);
+            if (use_ln) normalise(stage, g);
             __syncthreads();             // ... and everybody else's
             const int buf = stage & 1;
 #pragma unroll

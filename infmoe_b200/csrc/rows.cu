@@ -98,7 +98,8 @@ scatter_ln_split_kernel(long long T, int D, int vec, const float* __restrict__ X
 // fetched into registers by back-to-back 128-bit loads (NV per lane) before any of it is used, so it crosses HBM
 // once in one burst and both statistics passes and the split run from registers.  The additions happen in the
 // order of warp_row_stats, so the results are the same bits.  Few rows per SM (4096 rows on 148 SMs) would
-// otherwise leave the memory system half idle.
+// otherwise leave the memory system half idle.  The expert's LayerNorm weights are fetched into shared memory by
+// cp.async while the row is on its way, so the output loop never waits for L2.
 template <bool PACK, int NV>
 __global__ void __launch_bounds__(128)
 scatter_ln_split_reg_kernel(long long T, int D, const float* __restrict__ X, const float* __restrict__ score,
@@ -109,6 +110,8 @@ scatter_ln_split_reg_kernel(long long T, int D, const float* __restrict__ X, con
     const int lane = threadIdx.x & 31;
     const long long j = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (j >= T || (valid_rows && j >= *valid_rows)) return;
+    extern __shared__ __align__(16) float4 s_gamma_all[];     // [4 warps][NV * 32]
+    float4* s_gamma = s_gamma_all + (threadIdx.x >> 5) * (NV * 32);
     const int p = pos[j];
     const int e = gate[p];
     const float4* src = reinterpret_cast<const float4*>(X + (long long)p * D);
@@ -119,6 +122,15 @@ scatter_ln_split_reg_kernel(long long T, int D, const float* __restrict__ X, con
         const int base = 4 * lane + 128 * i;
         v[i] = base < D ? src[base >> 2] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int base = 4 * lane + 128 * i;
+        if (base < D) {
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_gamma + (base >> 2));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gamma + (base >> 2)) : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
@@ -141,13 +153,14 @@ scatter_ln_split_reg_kernel(long long T, int D, const float* __restrict__ X, con
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, 1e-6f)));
     uint16_t* pack_row = PACK ? reinterpret_cast<uint16_t*>(h_lo) + j * (long long)pack_pitch(D) : nullptr;
     const int k_end = PACK ? ((D + 31) & ~31) : D;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");   // every lane reads back only what it fetched itself
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int base = 4 * lane + 128 * i;
         if (base >= k_end) continue;
         float hh[4] = {0.f, 0.f, 0.f, 0.f}, ll[4] = {0.f, 0.f, 0.f, 0.f};
         if (base < D) {
-            const float4 g = gamma[base >> 2];
+            const float4 g = s_gamma[base >> 2];
             split_tf32(ln_apply(v[i].x, mean, rstd, g.x), hh[0], ll[0]);
             split_tf32(ln_apply(v[i].y, mean, rstd, g.y), hh[1], ll[1]);
             split_tf32(ln_apply(v[i].z, mean, rstd, g.z), hh[2], ll[2]);
@@ -327,8 +340,14 @@ int launch_scatter_ln_split(long long T, int D, const float* X, const float* sco
     if (vec && D <= 4096) {
         const unsigned grid = (unsigned)((T + 3) / 4);
 #define INFMOE_SCATTER_REG(PACK, NV)                                                                               \
-    scatter_ln_split_reg_kernel<PACK, NV><<<grid, 128, 0, stream>>>(T, D, X, score, pos, gate, gamma_all, valid_rows, \
-                                                                    routed, rscore, h_hi, h_lo)
+    do {                                                                                                           \
+        auto kern = scatter_ln_split_reg_kernel<PACK, NV>;                                                         \
+        constexpr int smem = 4 * NV * 32 * 16;                                                                     \
+        if (smem > 48 * 1024)                                                                                      \
+            INFMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));        \
+        kern<<<grid, 128, smem, stream>>>(T, D, X, score, pos, gate, gamma_all, valid_rows, routed, rscore, h_hi,  \
+                                          h_lo);                                                                   \
+    } while (0)
         if (pack) {
             if (D <= 1024) INFMOE_SCATTER_REG(true, 8);
             else if (D <= 2048) INFMOE_SCATTER_REG(true, 16);
