@@ -22,6 +22,7 @@
 #include <string>
 #include <vector>
 
+#include <sys/mman.h>
 #include <sys/stat.h>
 
 #include "common.cuh"
@@ -58,8 +59,14 @@ struct Flags {
 struct ExpertStore {
     int E = 0, D = 0, F = 0;
     std::mutex mu;
-    // pinned host copies of the raw FP32 weights (streaming mode source); nullptr if absent
+    // pinned host copies of the raw FP32 weights (streaming mode source); nullptr if absent.  A weight file is
+    // loaded into ONE page-locked arena (a single cudaHostAlloc instead of four per expert); weights given by
+    // pointer get allocations of their own.
     std::vector<float*> h_ln, h_wi0, h_wi1, h_wo;
+    char* h_arena = nullptr;
+    size_t arena_bytes = 0;
+    bool arena_registered = false;   // the arena is an anonymous mapping page-locked with cudaHostRegister
+    bool in_arena(const void* p) const { return h_arena && (const char*)p >= h_arena && (const char*)p < h_arena + arena_bytes; }
     std::vector<char> on_host;
     // device: LayerNorm weights of all experts [E][D] (always resident, 4*E*D bytes)
     float* d_ln = nullptr;
@@ -85,7 +92,11 @@ struct ExpertStore {
     ~ExpertStore() {
         for (auto& v : {&h_ln, &h_wi0, &h_wi1, &h_wo})
             for (float* p : *v)
-                if (p) cudaFreeHost(p);
+                if (p && !in_arena(p)) cudaFreeHost(p);
+        if (h_arena) {
+            if (arena_registered) cudaHostUnregister(h_arena);
+            munmap(h_arena, arena_bytes);
+        }
         if (d_ln) cudaFree(d_ln);
         for (float* p : d_plane)
             if (p) cudaFree(p);
@@ -564,6 +575,24 @@ int infmoe_layer_initialize(infmoe_layer* L) {
     }
     std::vector<int> seen((size_t)s->E, 0);
     const int D = s->D, F = s->F, E = s->E;
+    // one page-locked arena for the whole file: per expert [ln | wi_0 | wi_1 | wo], every tensor 256-byte aligned
+    const size_t ln_bytes = align_up(sizeof(float) * (size_t)D), mat_bytes = align_up(sizeof(float) * (size_t)D * F);
+    const size_t per_expert = ln_bytes + 3 * mat_bytes;
+    // The arena is an anonymous mapping that the reader threads fill (and thereby populate) in parallel; it is
+    // page-locked afterwards in one cudaHostRegister call.  Pinning memory that is already resident is several
+    // times faster than cudaHostAlloc followed by single-threaded first touches.
+    if (!s->h_arena) {
+        void* m = mmap(nullptr, per_expert * (size_t)E, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+        if (m == MAP_FAILED) {
+            set_error("cannot map %zu bytes of host memory for the expert weights", per_expert * (size_t)E);
+            return INFMOE_ERR_IO;
+        }
+        s->h_arena = (char*)m;
+        s->arena_bytes = per_expert * (size_t)E;
+    }
+    auto arena_slot = [&](long e, int k) -> float* {   // k: 0 ln, 1 wi_0, 2 wi_1, 3 wo
+        return (float*)(s->h_arena + per_expert * (size_t)e + (k == 0 ? 0 : ln_bytes + (size_t)(k - 1) * mat_bytes));
+    };
     auto alloc = [&](const std::string& name, const std::vector<int64_t>& shape, float** dst) -> int {
         *dst = nullptr;
         const size_t slash = name.find('/');
@@ -577,23 +606,35 @@ int infmoe_layer_initialize(infmoe_layer* L) {
         float** slot = nullptr;
         size_t want = 0;
         int bit = 0;
-        if (key == "layer_norm_weight") { slot = &s->h_ln[e]; want = (size_t)D; bit = 1; }
-        else if (key == "wi_0_weight") { slot = &s->h_wi0[e]; want = (size_t)D * F; bit = 2; }
-        else if (key == "wi_1_weight") { slot = &s->h_wi1[e]; want = (size_t)D * F; bit = 4; }
-        else if (key == "wo_weight") { slot = &s->h_wo[e]; want = (size_t)D * F; bit = 8; }
+        int kind = 0;
+        if (key == "layer_norm_weight") { slot = &s->h_ln[e]; want = (size_t)D; bit = 1; kind = 0; }
+        else if (key == "wi_0_weight") { slot = &s->h_wi0[e]; want = (size_t)D * F; bit = 2; kind = 1; }
+        else if (key == "wi_1_weight") { slot = &s->h_wi1[e]; want = (size_t)D * F; bit = 4; kind = 2; }
+        else if (key == "wo_weight") { slot = &s->h_wo[e]; want = (size_t)D * F; bit = 8; kind = 3; }
         else return INFMOE_OK;
         if (count != want) {  // reference: assert on num_bytes(), T5FFLayer.cc:61,68,75,82
             set_error("%s: %s has %zu elements, expected %zu", L->weight_file.c_str(), name.c_str(), count, want);
             return INFMOE_ERR_FORMAT;
         }
-        INFMOE_TRY(pinned_alloc(slot, want));
+        if (*slot && !s->in_arena(*slot)) cudaFreeHost(*slot);   // an expert given by pointer before: the file wins
+        *slot = arena_slot(e, kind);
         *dst = *slot;
         seen[e] |= bit;
         return INFMOE_OK;
     };
     bool fortran = false;
-    INFMOE_TRY(npz_read(L->weight_file.c_str(), alloc, &fortran));
+    // the members are independent ranges of the file: read (and inflate) them with a few threads at once
+    static const int threads = [] {
+        const char* v = getenv("INFMOE_LOAD_THREADS");
+        const int n = v ? atoi(v) : 8;
+        return n < 1 ? 1 : (n > 64 ? 64 : n);
+    }();
+    INFMOE_TRY(npz_read(L->weight_file.c_str(), alloc, &fortran, threads));
     s->fortran_warning = fortran;
+    if (!s->arena_registered) {
+        INFMOE_CUDA_TRY(cudaHostRegister(s->h_arena, s->arena_bytes, cudaHostRegisterPortable));
+        s->arena_registered = true;
+    }
     for (int e = 0; e < E; ++e) {
         if (seen[e] != 15) {
             set_error("%s: expert %d is missing tensors (mask 0x%x of 0xf)", L->weight_file.c_str(), e, seen[e]);

@@ -14,12 +14,16 @@
 // relative to the reference.  A warning is printed once per file.
 #include "npz.h"
 
+#include <fcntl.h>
+#include <unistd.h>
 #include <zlib.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdint>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -128,9 +132,69 @@ class Member {
     std::vector<uint8_t> buf_;
 };
 
+// One member whose data is read after the walk, by a worker thread with a file descriptor of its own.
+struct Job {
+    std::string name;
+    bool deflated = false;
+    uint64_t offset = 0;       // stored: first payload byte; deflated: first byte of the compressed stream
+    uint64_t comp_size = 0;    // deflated: compressed bytes
+    size_t skip = 0;           // deflated: uncompressed bytes before the payload (the npy header)
+    size_t bytes = 0;          // payload bytes
+    float* dst = nullptr;
+};
+
+bool pread_exact(int fd, void* dst, size_t n, uint64_t off) {
+    uint8_t* p = (uint8_t*)dst;
+    while (n) {
+        const ssize_t got = pread(fd, p, n < (1u << 30) ? n : (1u << 30), (off_t)off);
+        if (got <= 0) return false;
+        p += got;
+        off += (uint64_t)got;
+        n -= (size_t)got;
+    }
+    return true;
+}
+
+bool run_job(int fd, const Job& j) {
+    if (!j.deflated) return pread_exact(fd, j.dst, j.bytes, j.offset);
+    z_stream z;
+    memset(&z, 0, sizeof(z));
+    if (inflateInit2(&z, -MAX_WBITS) != Z_OK) return false;
+    std::vector<uint8_t> in(1 << 20), head(j.skip ? j.skip : 1);
+    uint64_t off = j.offset, left = j.comp_size;
+    bool ok = true;
+    // two output segments: the npy header (discarded), then the payload
+    for (int seg = 0; seg < 2 && ok; ++seg) {
+        uint8_t* out = seg == 0 ? head.data() : (uint8_t*)j.dst;
+        size_t want = seg == 0 ? j.skip : j.bytes, done = 0;
+        while (done < want) {
+            if (z.avail_in == 0) {
+                const size_t chunk = left < in.size() ? (size_t)left : in.size();
+                if (chunk == 0 || !pread_exact(fd, in.data(), chunk, off)) { ok = false; break; }
+                off += chunk;
+                left -= chunk;
+                z.next_in = in.data();
+                z.avail_in = (uInt)chunk;
+            }
+            const size_t room = want - done < (1u << 30) ? want - done : (1u << 30);
+            z.next_out = out + done;
+            z.avail_out = (uInt)room;
+            const int rc = inflate(&z, Z_NO_FLUSH);
+            done += room - z.avail_out;
+            if (rc == Z_STREAM_END) break;
+            if (rc != Z_OK) { ok = false; break; }
+        }
+        ok = ok && done == want;
+    }
+    inflateEnd(&z);
+    return ok;
+}
+
 }  // namespace
 
-int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order) {
+int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order, int threads) {
+    std::vector<Job> jobs;
+    const bool deferred = threads > 1;
     File file;
     file.f = fopen(path, "rb");
     if (!file.f) {
@@ -180,6 +244,7 @@ int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order)
         }
         if (name.size() > 4 && name.compare(name.size() - 4, 4, ".npy") == 0) name.resize(name.size() - 4);
 
+        const uint64_t member_start = (uint64_t)ftello(file.f);
         Member m(file.f, method == 8, comp_size);
         uint8_t pre[10];
         if (!m.read(pre, 10) || memcmp(pre, "\x93NUMPY", 6) != 0) {
@@ -230,7 +295,18 @@ int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order)
         float* dst = nullptr;
         const int rc = alloc(name, shape, &dst);
         if (rc != INFMOE_OK) return rc;
-        if (dst) {
+        if (dst && deferred) {
+            Job j;
+            j.name = name;
+            j.deflated = method == 8;
+            j.offset = j.deflated ? member_start : (uint64_t)ftello(file.f);
+            j.comp_size = comp_size;
+            j.skip = (pre[6] >= 2 ? 12 : 10) + hlen;
+            j.bytes = count * sizeof(float);
+            j.dst = dst;
+            jobs.push_back(j);
+            if (method == 0 && fseeko(file.f, (off_t)(count * sizeof(float)), SEEK_CUR) != 0) return INFMOE_ERR_IO;
+        } else if (dst) {
             if (!m.read(dst, count * sizeof(float))) {
                 set_error("%s: member %s is truncated", path, name.c_str());
                 return INFMOE_ERR_FORMAT;
@@ -247,6 +323,32 @@ int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order)
             const size_t rest = (sig ? 4 : 0) + (comp_size > 0xFFFFFFFEull ? 16 : 8);
             if (fseeko(file.f, (off_t)rest, SEEK_CUR) != 0) return INFMOE_ERR_IO;
         }
+    }
+    if (jobs.empty()) return INFMOE_OK;
+    // The members' data, read (and inflated) by a few threads at once: every member is an independent range of
+    // the file, and one thread neither saturates the storage nor, for deflated files, the decompressor.
+    const int n = (int)jobs.size() < threads ? (int)jobs.size() : threads;
+    std::atomic<size_t> next{0};
+    std::atomic<int> failed{-1};
+    auto worker = [&]() {
+        const int fd = open(path, O_RDONLY);
+        if (fd < 0) {
+            failed.store((int)jobs.size());
+            return;
+        }
+        for (size_t i; (i = next.fetch_add(1)) < jobs.size() && failed.load() < 0;)
+            if (!run_job(fd, jobs[i])) failed.store((int)i);
+        close(fd);
+    };
+    std::vector<std::thread> pool;
+    for (int t = 1; t < n; ++t) pool.emplace_back(worker);
+    worker();
+    for (auto& t : pool) t.join();
+    const int bad = failed.load();
+    if (bad >= 0) {
+        if (bad >= (int)jobs.size()) set_error("cannot open weight file %s", path);
+        else set_error("%s: member %s is truncated or corrupt", path, jobs[(size_t)bad].name.c_str());
+        return bad >= (int)jobs.size() ? INFMOE_ERR_IO : INFMOE_ERR_FORMAT;
     }
     return INFMOE_OK;
 }

@@ -13,6 +13,9 @@ namespace infmoe {
 // A non-zero return aborts the read with that status.
 using NpzAllocFn = std::function<int(const std::string& name, const std::vector<int64_t>& shape, float** dst)>;
 
-int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order);
+// threads <= 1: every member's data is read before the next alloc call (a caller may consume it there).
+// threads > 1: the walk only hands out destinations; the data is read afterwards by that many threads, each
+// with a file descriptor of its own, and is complete when the function returns.
+int npz_read(const char* path, const NpzAllocFn& alloc, bool* saw_fortran_order, int threads = 1);
 
 }  // namespace infmoe

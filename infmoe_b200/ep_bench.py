@@ -56,6 +56,29 @@ def _parity(total, x_local, out_local, gate_local, score_local, dev, torch, rows
             "ok": bool(gate_equal and worst <= 1e-5 and np.isfinite(out_local).all())}
 
 
+def _bind_to_gpu_numa_node(torch, local_rank):
+    """Runs this rank on the CPUs of its GPU's NUMA node (when the node and its CPUs can be read and some of them
+    are available to the process), so that the page-locked host buffers it allocates next are local to the GPU.
+    -> a short description for the result line."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return "numa node unknown"
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        usable = cpus & os.sched_getaffinity(0)
+        if not usable:
+            return f"gpu on numa node {node}, none of its cpus available to this process"
+        os.sched_setaffinity(0, usable)
+        return f"bound to {len(usable)} cpus of numa node {node}"
+    except (OSError, ValueError, AttributeError) as exc:
+        return f"not bound ({type(exc).__name__})"
+
+
 def _measure(total, scaling, steps, warmup, torch, dist, dev, rank, world, peaks, clock_sampler_cls, local_rank,
              gemm_roofline, with_e2e=True):
     """Builds this rank's share of workload `total`, times it, checks rank 0's result.  -> dict (rank 0) or None."""
@@ -182,6 +205,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
     if not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     peaks = peaks_fn()
+    numa = _bind_to_gpu_numa_node(torch, local_rank)
     warmup = max(args.warmup, 3)
     main = _measure(total, scaling, args.steps, warmup, torch, dist, dev, rank, world, peaks, clock_sampler_cls,
                     local_rank, gemm_roofline)
@@ -221,7 +245,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
                     "h2d_bytes_per_step": main["hx_bytes"] * world, "d2h_bytes_per_step": main["hx_bytes"] * world,
                     "ms_per_step": e2e["ms"], "h2d_gbs_per_rank_min": e2e["h2d_gbs_per_rank_min"],
                     "d2h_gbs_per_rank_min": e2e["d2h_gbs_per_rank_min"],
-                    "same_bits_as_device_path": e2e["same_bits_as_device_path"]},
+                    "same_bits_as_device_path": e2e["same_bits_as_device_path"], "host_placement_rank0": numa},
             "gpu_launches": main["launches"], "stage_ms_rank0": main["stage_ms_rank0"],
             "phase_ms_rank0": main["phase_ms_rank0"], "rows_received_rank0": main["rows_received_rank0"],
             "parity": main["parity"], "roofline": main["roofline"], "cpu_baseline": None, "clocks": main["clocks"],

@@ -10,6 +10,8 @@ configure_plugin, get_workspace_size, enqueue, serialize, clone, terminate.
 from __future__ import annotations
 
 import ctypes
+import os
+import sys
 from typing import Optional, Sequence
 
 import numpy as np
@@ -17,8 +19,43 @@ import numpy as np
 from . import capi
 from .config import MoELayerConfig
 
+try:  # optional: the reference imports TensorRT unconditionally (python/infmoe/plugin.py:6)
+    import tensorrt as trt  # type: ignore
+except ImportError:  # pragma: no cover - depends on the installation
+    trt = None
+
 PLUGIN_NAME = "MoELayerPlugin"
 PLUGIN_VERSION = "1"
+
+
+def search_library(lib_name: str = "libtrtmoelayer.so") -> str:
+    """The TensorRT plugin library, looked for where the reference looks (python/infmoe/plugin.py:14-29): the
+    plugin's build directory first, then ./build beside this package, then the package directory itself."""
+    here = os.path.dirname(os.path.realpath(__file__))
+    for d in (os.path.join(here, "../../plugin/builddir"), os.path.join(here, "build"), here):
+        path = os.path.join(d, lib_name)
+        if os.path.isfile(path):
+            print(f"Loaded library {path}", file=sys.stderr)
+            sys.stderr.flush()
+            return path
+    raise Exception(f"Cannot find {lib_name}, have you run python -m infmoe_b200.build?")
+
+
+_TRT_STATE = {}
+
+
+def _trt_creator(namespace: str):
+    """Loads libtrtmoelayer.so (its static registration runs on dlopen) and asks TensorRT's registry for the
+    creator, like the reference's module-level code (python/infmoe/plugin.py:32-58)."""
+    if "lib" not in _TRT_STATE:
+        _TRT_STATE["lib"] = ctypes.CDLL(search_library())
+        _TRT_STATE["logger"] = trt.Logger(trt.Logger.WARNING)
+        trt.init_libnvinfer_plugins(_TRT_STATE["logger"], "")
+    creator = trt.get_plugin_registry().get_plugin_creator(PLUGIN_NAME, PLUGIN_VERSION, namespace)
+    if creator is None:
+        raise Exception("Cannot initialize creator for MoELayerPlugin: check that libtrtmoelayer.so was loaded and "
+                        "that it was built against the TensorRT version of the tensorrt Python package")
+    return creator
 
 
 def _fptr(a: Optional[np.ndarray]):
@@ -320,7 +357,37 @@ class MoELayerPlugin:
     def set_config(self, config: MoELayerConfig):
         self.config = config
 
-    def create_plugin(self, plugin_name='moe_layer_plugin') -> MoELayer:
+    def create_trt_plugin(self, plugin_name='moe_layer_plugin'):
+        """The TensorRT IPluginV2 object, created through TensorRT's plugin registry from the nine attributes
+        (python/infmoe/plugin.py:92-119 and :73-75 of the reference).  Needs the tensorrt package."""
+        if trt is None:
+            raise ImportError("the tensorrt Python package is not installed; create_plugin() gives the same layer "
+                              "through the C ABI")
+        c = self.__config
+        if c is None:
+            raise Exception('No MoE config provided')
+        self._encoded = [c.weight_file_path.encode('utf-8'), c.sublayer_type.encode('utf-8'),
+                         c.moe_variant.encode('utf-8')]
+        fields = [
+            trt.PluginField("expert_count", np.int32(c.expert_count), trt.PluginFieldType.INT32),
+            trt.PluginField("embedding_size", np.int32(c.embedding_size), trt.PluginFieldType.INT32),
+            trt.PluginField("hidden_size", np.int32(c.hidden_size), trt.PluginFieldType.INT32),
+            trt.PluginField("max_concurrency", np.int32(c.max_concurrency), trt.PluginFieldType.INT32),
+            trt.PluginField("expert_centroids", c.expert_centroids, trt.PluginFieldType.FLOAT32),
+            trt.PluginField("expert_weight_file", self._encoded[0], trt.PluginFieldType.UNKNOWN),
+            trt.PluginField("expert_sublayer_type", self._encoded[1], trt.PluginFieldType.UNKNOWN),
+            trt.PluginField("moe_variant", self._encoded[2], trt.PluginFieldType.UNKNOWN),
+        ]
+        if c.layernorm_weight is not None:
+            fields.append(trt.PluginField("layernorm_weight", c.layernorm_weight, trt.PluginFieldType.FLOAT32))
+        return _trt_creator(self.namespace).create_plugin(plugin_name, trt.PluginFieldCollection(fields))
+
+    def create_plugin(self, plugin_name='moe_layer_plugin'):
+        """The plugin object for `config`.  With INFMOE_USE_TENSORRT=1 and the tensorrt package installed this is
+        the TensorRT plugin from the registry, as in the reference; otherwise a `MoELayer` over the C ABI with
+        the same life cycle, which needs no TensorRT."""
+        if trt is not None and os.environ.get("INFMOE_USE_TENSORRT", "0") == "1":
+            return self.create_trt_plugin(plugin_name)
         c = self.__config
         if c is None:
             raise Exception('No MoE config provided')

@@ -67,6 +67,23 @@ def test_tiny_layer_from_npz(torch_cuda, oracle, tmp_path, variant):
     layer.terminate()
 
 
+def test_compressed_weight_file_loads_to_the_same_layer(torch_cuda, oracle, tmp_path):
+    """initialize() reads the members of the npz with several threads into one page-locked arena; a deflated file
+    (np.savez_compressed) and a stored one must give the same layer."""
+    from infmoe_b200 import MoELayer, synth
+    w = synth.scaled(synth.WORKLOADS["cpm2"], expert_count=12, embedding_size=128, hidden_size=384, batch=1, seq_len=200)
+    x, c, ln = synth.gen_inputs(w)
+    experts = [synth.gen_expert_numpy(w, e) for e in range(w.expert_count)]
+    outs = []
+    for compressed in (False, True):
+        path = synth.write_npz(w, str(tmp_path / f"w{int(compressed)}.npz"), compressed=compressed)
+        layer = MoELayer.create(w.expert_count, w.embedding_size, w.hidden_size, 2, c, path, "T5_FF", w.variant, ln)
+        layer.initialize()
+        outs.append(_check(layer, w, x, c, ln, experts, oracle, torch_cuda))
+        layer.terminate()
+    np.testing.assert_array_equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("name,kw", [
     ("cpm2", dict(expert_count=8, embedding_size=512, hidden_size=1024, batch=2, seq_len=300)),
     ("base_layer_zipf", dict(expert_count=16, embedding_size=256, hidden_size=512, batch=4, seq_len=256)),
