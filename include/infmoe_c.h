@@ -83,6 +83,11 @@ INFMOE_API int infmoe_layer_initialize(infmoe_layer* layer);
 INFMOE_API int infmoe_layer_set_expert(infmoe_layer* layer, int32_t expert, const float* ln_w, const float* wi0,
                                        const float* wi1, const float* wo, int on_device);
 
+/* For a layer that holds a contiguous share of a larger layer's experts (one rank of an expert-parallel layer):
+ * expert n of this layer is expert first_expert + n of the weight file; infmoe_layer_initialize then reads only
+ * those.  No reference counterpart (single GPU). */
+INFMOE_API int infmoe_layer_set_file_expert_offset(infmoe_layer* layer, int32_t first_expert);
+
 /* Residency of expert weights.  mode 0: stream every used expert from pinned
  * host memory on every call through max_concurrency slots, like the reference
  * (plugin/MoELayerPlugin.cc:360-394); mode 1: keep all experts in device
@@ -186,6 +191,35 @@ INFMOE_API int infmoe_layer_deserialize(const void* h_buffer, size_t bytes, infm
 INFMOE_API int infmoe_weight_file_check(const char* path, int32_t expert_count, int32_t embedding_size,
                                         int32_t hidden_size, double* h_sums);
 
+/* Custom expert sublayers: the C form of deriving from MoESubLayer (plugin/sublayers/SubLayer.h:18-48) and adding
+ * a case to MoELayerPlugin::createSublayer (plugin/MoELayerPlugin.cc:28-41; README "custom sublayer").  A type
+ * registered here can be named in expert_sublayer_type.  The layer then routes, dispatches and scatters as for
+ * the built-in types, and for every expert that has rows calls copy_weights into one of max_concurrency device
+ * slots (on a copy stream, while the expert before it runs) and run on the caller's stream; the combine step
+ * follows.  One host synchronisation per call (the token counts), like the streamed built-in experts.  The copy
+ * stream handed to copy_weights belongs to the layer and is destroyed with it: a callback must not leave anything
+ * behind that refers to it later (an allocator that remembers which streams used a buffer, for instance). */
+typedef struct infmoe_sublayer_vtable {
+    void* user;                                    /* passed back to every callback */
+    /* MoESubLayer::initialize (SubLayer.h:44): read weights etc.; called by infmoe_layer_initialize.  May be NULL. */
+    int (*initialize)(void* user, int32_t expert_count, int32_t embedding_size, int32_t hidden_size,
+                      const char* weight_file);
+    /* MoESubLayer::weightSize (:36): bytes of one expert's weights in a device slot; NULL or 0 = no slots. */
+    size_t (*weight_size)(void* user);
+    /* MoESubLayer::workspaceSize (:37): scratch bytes run needs for token_count rows.  May be NULL. */
+    size_t (*workspace_size)(void* user, int32_t token_count);
+    /* MoESubLayer::copyWeights (:39): enqueue the copy of expert `expert`'s weights to d_dst on `stream`. */
+    int (*copy_weights)(void* user, void* d_dst, int32_t expert, void* stream);
+    /* MoESubLayer::run (:40-41): d_output[token_count][embedding_size] = the expert applied to d_input, enqueued on
+     * `stream` (it need not, and should not, synchronise); 0 = ok.  Required. */
+    int (*run)(void* user, int32_t expert, int32_t token_count, const void* d_weights, const float* d_input,
+               float* d_output, void* d_workspace, void* stream);
+} infmoe_sublayer_vtable;
+
+/* Registers (or replaces) a sublayer type for this process.  The callbacks must stay valid while layers of the
+ * type exist; layers created before a re-registration keep the callbacks they were created with. */
+INFMOE_API int infmoe_register_sublayer(const char* type_name, const infmoe_sublayer_vtable* vt);
+
 /* Read-back of the attributes (for the plugin classes and the Python binding). */
 INFMOE_API int infmoe_layer_get_config(const infmoe_layer* layer, infmoe_layer_config* out);
 
@@ -222,6 +256,12 @@ INFMOE_API int infmoe_ep_unique_id(void* h_id);
 /* Collective over all ranks: creates the communicator, allocates the buffers and maps the peers' with CUDA IPC
  * (peer access between the GPUs is required).  Uses the current device. */
 INFMOE_API int infmoe_ep_create(const infmoe_ep_config* cfg, infmoe_ep** out);
+/* The same from the configuration of the WHOLE layer (what the plugin creator holds): creates this rank's layer
+ * object (experts rank * E/world ..., read from the same weight file), initializes it, and wraps it.  *local_out
+ * is owned by the caller and must outlive *ep_out. */
+INFMOE_API int infmoe_ep_create_sharded(const infmoe_layer_config* whole_layer, int32_t rank, int32_t world,
+                                        const void* unique_id, int64_t max_tokens, infmoe_layer** local_out,
+                                        infmoe_ep** ep_out);
 /* One layer pass for this rank's `tokens` rows (collective, stream ordered, does not block the host).
  * d_out may be the pointer infmoe_ep_output returns (or NULL): then the result is left in that buffer and no copy
  * is made.  Device-side findings are returned by infmoe_ep_sync_status. */

@@ -67,6 +67,27 @@ class EpConfig(ctypes.Structure):
 
 EP_ID_BYTES = 128
 
+SUB_INIT_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p)
+SUB_WEIGHT_SIZE_FN = ctypes.CFUNCTYPE(ctypes.c_size_t, ctypes.c_void_p)
+SUB_WS_SIZE_FN = ctypes.CFUNCTYPE(ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int32)
+SUB_COPY_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p)
+SUB_RUN_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p)
+
+
+class SublayerVtable(ctypes.Structure):
+    """struct infmoe_sublayer_vtable"""
+
+    _fields_ = [
+        ("user", ctypes.c_void_p),
+        ("initialize", SUB_INIT_FN),
+        ("weight_size", SUB_WEIGHT_SIZE_FN),
+        ("workspace_size", SUB_WS_SIZE_FN),
+        ("copy_weights", SUB_COPY_FN),
+        ("run", SUB_RUN_FN),
+    ]
+
+
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int32
@@ -79,6 +100,7 @@ SIGNATURES = {
     "infmoe_layer_initialize": [_vp],
     "infmoe_layer_set_expert": [_vp, _i32, _vp, _vp, _vp, _vp, ctypes.c_int],
     "infmoe_layer_set_residency": [_vp, ctypes.c_int],
+    "infmoe_layer_set_file_expert_offset": [_vp, _i32],
     "infmoe_layer_set_expert_cache": [_vp, _i32],
     "infmoe_layer_weight_h2d_bytes": [_vp, ctypes.POINTER(ctypes.c_uint64)],
     "infmoe_expert_cache_simulate": [_i32, _i32, _vp, _vp, _i32, _vp],
@@ -111,8 +133,11 @@ SIGNATURES = {
     "infmoe_t5ff_run": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp],
     "infmoe_t5ff_static_limit": [_i64, _i32, _i32, ctypes.POINTER(_sz), ctypes.POINTER(_sz)],
     "infmoe_t5ff_run_static": [_i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "infmoe_register_sublayer": [ctypes.c_char_p, ctypes.POINTER(SublayerVtable)],
     "infmoe_ep_unique_id": [_vp],
     "infmoe_ep_create": [ctypes.POINTER(EpConfig), ctypes.POINTER(_vp)],
+    "infmoe_ep_create_sharded": [ctypes.POINTER(LayerConfig), _i32, _i32, _vp, _i64, ctypes.POINTER(_vp),
+                                 ctypes.POINTER(_vp)],
     "infmoe_ep_create_loopback": [ctypes.POINTER(EpConfig), _i32, ctypes.POINTER(_vp)],
     "infmoe_ep_forward": [_vp, _vp, _vp, _i64, _vp],
     "infmoe_ep_forward_begin": [_vp, _vp, _i64, _vp],

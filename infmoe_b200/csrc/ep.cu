@@ -502,6 +502,49 @@ int infmoe_ep_create(const infmoe_ep_config* c, infmoe_ep** out) {
     return INFMOE_OK;
 }
 
+int infmoe_ep_create_sharded(const infmoe_layer_config* whole, int32_t rank, int32_t world, const void* unique_id,
+                             int64_t max_tokens, infmoe_layer** local_out, infmoe_ep** ep_out) {
+    if (!whole || !local_out || !ep_out || world <= 0 || rank < 0 || rank >= world || whole->expert_count <= 0 ||
+        whole->expert_count % world != 0 || !whole->expert_centroids) {
+        set_error("ep_create_sharded: bad argument (expert_count must be divisible by world)");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    *local_out = nullptr;
+    *ep_out = nullptr;
+    const int per = whole->expert_count / world, lo = rank * per;
+    infmoe_layer_config lc = *whole;
+    lc.expert_count = per;
+    lc.expert_centroids = whole->expert_centroids + (size_t)lo * whole->embedding_size;   // unused by the experts
+    lc.layernorm_weight = nullptr;
+    lc.moe_variant = "default";   // routing and the output mix are the wrapper's; the local layer only runs experts
+    infmoe_layer* local = nullptr;
+    INFMOE_TRY(infmoe_layer_create(&lc, &local));
+    int rc = infmoe_layer_set_file_expert_offset(local, lo);
+    if (rc == INFMOE_OK) rc = infmoe_layer_initialize(local);
+    if (rc == INFMOE_OK) rc = infmoe_layer_set_residency(local, 1);
+    infmoe_ep_config ec{};
+    ec.rank = rank;
+    ec.world = world;
+    ec.unique_id = unique_id;
+    ec.expert_count = whole->expert_count;
+    ec.embedding_size = whole->embedding_size;
+    ec.hidden_size = whole->hidden_size;
+    ec.max_tokens = max_tokens;
+    ec.expert_centroids = whole->expert_centroids;
+    ec.layernorm_weight = whole->layernorm_weight;
+    ec.moe_variant = whole->moe_variant;
+    ec.local_experts = local;
+    infmoe_ep* ep = nullptr;
+    if (rc == INFMOE_OK) rc = infmoe_ep_create(&ec, &ep);
+    if (rc != INFMOE_OK) {
+        infmoe_layer_destroy(local);
+        return rc;
+    }
+    *local_out = local;
+    *ep_out = ep;
+    return INFMOE_OK;
+}
+
 int infmoe_ep_create_loopback(const infmoe_ep_config* configs, int32_t world, infmoe_ep** outs) {
     if (!configs || !outs || world <= 0 || world > EP_MAX_WORLD) {
         set_error("ep_create_loopback: bad argument");

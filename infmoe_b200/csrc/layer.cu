@@ -17,6 +17,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -106,8 +107,17 @@ struct ExpertStore {
 };
 
 struct WsLayout {
-    size_t gate, pos, count, offset, slot_map, score, rscore, routed, post, h_hi, h_lo, g_hi, g_lo, slots, total;
+    size_t gate, pos, count, offset, slot_map, score, rscore, routed, post, h_hi, h_lo, g_hi, g_lo, slots, custom_slots,
+        custom_ws, total;
 };
+
+// Sublayer types registered through infmoe_register_sublayer (the reference's extension point is deriving from
+// MoESubLayer and adding a case to createSublayer, plugin/MoELayerPlugin.cc:28-41).
+std::mutex g_sublayer_mu;
+std::map<std::string, infmoe_sublayer_vtable>& sublayer_registry() {
+    static std::map<std::string, infmoe_sublayer_vtable> r;
+    return r;
+}
 
 }  // namespace
 }  // namespace infmoe
@@ -119,7 +129,11 @@ struct infmoe_layer {
     std::vector<float> centroids, gating_ln;
     std::string weight_file, sublayer_type, variant;
     Flags flags;
+    int file_expert_offset = 0;          // expert n of this layer is expert file_expert_offset + n of the weight file
     bool identity = false;
+    bool custom = false;                 // a registered sublayer type; `sub` holds its callbacks
+    infmoe_sublayer_vtable sub{};
+    bool sub_initialized = false;
     std::shared_ptr<ExpertStore> store;
     int residency = -1;          // -1 auto, 0 streamed, 1 resident
     bool residency_resolved = false;
@@ -215,16 +229,20 @@ WsLayout ws_layout(const infmoe_layer* L, long long T, bool streamed) {
     w.rscore = take(4 * t);
     // The tensor-core GEMM reads its residual from the input through pos[] and writes the layer output from its
     // epilogue; only the CUDA-core path and the Identity sublayer keep routed rows and expert-ordered results.
-    const bool row_planes = L->identity || !uses_umma(L);
+    const bool row_planes = L->identity || L->custom || !uses_umma(L);
     w.routed = take(row_planes ? 4 * t * D : 0);
     w.post = take(row_planes ? 4 * t * D : 0);
     w.h_hi = take(4 * t * D);
     w.h_lo = take(second_plane_bytes((long long)t, L->D));
     w.g_hi = take(4 * t * F);
     w.g_lo = take(second_plane_bytes((long long)t, L->F));
-    w.slots = take(streamed && !L->identity
+    w.slots = take(streamed && !L->identity && !L->custom
                        ? 4 * (size_t)L->mc * (tiled_elems(2 * L->F, L->D) + tiled_elems(L->D, L->F) + 3 * D * F)
                        : 0);
+    // registered sublayer: max_concurrency weight slots (MoESubLayer::weightSize each) and its own scratch
+    const size_t sub_weight = L->custom && L->sub.weight_size ? align_up(L->sub.weight_size(L->sub.user)) : 0;
+    w.custom_slots = take(sub_weight * (size_t)L->mc);
+    w.custom_ws = take(L->custom && L->sub.workspace_size ? L->sub.workspace_size(L->sub.user, (int32_t)T) : 0);
     w.total = o;
     return w;
 }
@@ -498,9 +516,17 @@ int infmoe_layer_create(const infmoe_layer_config* cfg, infmoe_layer** out) {
     }
     const char* type = cfg->expert_sublayer_type ? cfg->expert_sublayer_type : "T5_FF";
     const bool identity = strcmp(type, "Identity") == 0;
+    bool custom = false;
+    infmoe_sublayer_vtable sub{};
     if (!identity && strcmp(type, "T5_FF") != 0) {
-        set_error("unsupported sublayer type: %s", type);  // plugin/MoELayerPlugin.cc:37-39
-        return INFMOE_ERR_INVALID_ARGUMENT;
+        std::lock_guard<std::mutex> lock(g_sublayer_mu);
+        auto it = sublayer_registry().find(type);
+        if (it == sublayer_registry().end()) {
+            set_error("unsupported sublayer type: %s", type);  // plugin/MoELayerPlugin.cc:37-39
+            return INFMOE_ERR_INVALID_ARGUMENT;
+        }
+        custom = true;
+        sub = it->second;
     }
     if (cfg->expert_weight_file && *cfg->expert_weight_file) {
         struct stat st;
@@ -521,6 +547,8 @@ int infmoe_layer_create(const infmoe_layer_config* cfg, infmoe_layer** out) {
     L->variant = cfg->moe_variant;
     L->flags = flags;
     L->identity = identity;
+    L->custom = custom;
+    L->sub = sub;
     L->store = make_store(L->E, L->D, L->F);
     L->launches_at_create = g_kernel_launches;
     // decided here, not at the first enqueue: the workspace size depends on it
@@ -546,7 +574,11 @@ int infmoe_layer_clone(const infmoe_layer* src, infmoe_layer** out) {
     L->sublayer_type = src->sublayer_type;
     L->variant = src->variant;
     L->flags = src->flags;
+    L->file_expert_offset = src->file_expert_offset;
     L->identity = src->identity;
+    L->custom = src->custom;
+    L->sub = src->sub;
+    L->sub_initialized = src->sub_initialized;
     L->store = src->store;  // shared, like the reference's sublayer
     L->residency = src->residency;
     L->initialized = src->initialized;
@@ -560,6 +592,18 @@ int infmoe_layer_initialize(infmoe_layer* L) {
     if (!L) {
         set_error("layer_initialize: null layer");
         return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (L->custom) {   // MoESubLayer::initialize (sublayers/SubLayer.h:44)
+        if (!L->sub_initialized && L->sub.initialize) {
+            const int rc = L->sub.initialize(L->sub.user, L->E, L->D, L->F, L->weight_file.c_str());
+            if (rc != 0) {
+                set_error("sublayer %s: initialize failed with %d", L->sublayer_type.c_str(), rc);
+                return INFMOE_ERR_STATE;
+            }
+        }
+        L->sub_initialized = true;
+        L->initialized = true;
+        return INFMOE_OK;
     }
     if (L->identity || L->weight_file.empty()) {
         L->initialized = true;
@@ -598,7 +642,8 @@ int infmoe_layer_initialize(infmoe_layer* L) {
         const size_t slash = name.find('/');
         if (slash == std::string::npos) return INFMOE_OK;  // not an expert tensor: ignored like the reference
         char* endp = nullptr;
-        const long e = strtol(name.c_str(), &endp, 10);
+        const long e_file = strtol(name.c_str(), &endp, 10);
+        const long e = e_file - L->file_expert_offset;   // experts outside this layer's share are skipped
         if (endp != name.c_str() + slash || e < 0 || e >= E) return INFMOE_OK;
         const std::string key = name.substr(slash + 1);
         size_t count = 1;
@@ -682,6 +727,15 @@ int infmoe_layer_set_expert(infmoe_layer* L, int32_t e, const float* ln_w, const
         s->ln_on_device[e] = 0;
     }
     L->initialized = true;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_set_file_expert_offset(infmoe_layer* L, int32_t first_expert) {
+    if (!L || first_expert < 0) {
+        set_error("layer_set_file_expert_offset: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    L->file_expert_offset = first_expert;
     return INFMOE_OK;
 }
 
@@ -897,7 +951,14 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     cudaStream_t stream = (cudaStream_t)stream_v;
     ExpertStore* s = L->store.get();
     INFMOE_TRY(ensure_device(L));
-    if (!L->identity) {
+    if (L->custom) {
+        if (!L->sub_initialized) {
+            set_error("layer_enqueue: sublayer %s is not initialized (call infmoe_layer_initialize first)",
+                      L->sublayer_type.c_str());
+            return INFMOE_ERR_STATE;
+        }
+        L->resident = false;
+    } else if (!L->identity) {
         std::lock_guard<std::mutex> lock(s->mu);
         for (int e = 0; e < s->E; ++e) {
             if (!s->on_host[e] && !s->on_device[e]) {
@@ -911,7 +972,7 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     } else {
         L->resident = true;
     }
-    const bool streamed = !L->resident;
+    const bool streamed = !L->resident && !L->custom;
     const WsLayout w = ws_layout(L, T, streamed);
     char* base = (char*)(((uintptr_t)d_ws + ALIGN - 1) / ALIGN * ALIGN);
     if ((size_t)(base - (char*)d_ws) + w.total > ws_bytes) {
@@ -952,7 +1013,7 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
     // whole layer: the variant decides; experts alone: the caller asks for the mix by passing the scores
     const bool mix = given_gate ? row_score != nullptr : L->flags.base_layer_mix;
     // the tensor-core GEMM writes the layer output itself (combine fused into its epilogue)
-    const bool fused_combine = !L->identity && uses_umma(L);
+    const bool fused_combine = !L->identity && !L->custom && uses_umma(L);
     FfnOutput ffn_out;
     ffn_out.post = post;
     if (fused_combine) {
@@ -965,6 +1026,51 @@ static int layer_run(infmoe_layer* L, const float* d_in, float* d_out, void* d_w
         // Identity expert (plugin/sublayers/IdentityLayer.hh): post = routed
         INFMOE_TRY(launch_scatter(T, L->D, d_in, score, pos, routed, rscore, stream));
         INFMOE_CUDA_TRY(cudaMemcpyAsync(post, routed, sizeof(float) * (size_t)T * L->D, cudaMemcpyDeviceToDevice, stream));
+    } else if (L->custom) {
+        // A registered sublayer, driven the way the reference drives any MoESubLayer (plugin/MoELayerPlugin.cc:
+        // 360-402): for every expert that has rows, its weights go into slot j % max_concurrency on a copy stream
+        // while the expert before it runs, then run() on the caller's stream.  One host synchronisation (the
+        // token counts), everything after it chained by events.
+        INFMOE_TRY(launch_scatter(T, L->D, d_in, score, pos, routed, rscore, stream));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_count, count, sizeof(int) * L->E, cudaMemcpyDeviceToHost, stream));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+        INFMOE_CUDA_TRY(cudaStreamSynchronize(stream));
+        if (*L->h_status) {
+            const int st = *L->h_status;
+            cudaMemsetAsync(L->d_status, 0, sizeof(int), stream);
+            *L->h_status = 0;
+            return status_to_rc(st);
+        }
+        const size_t slot_bytes = L->sub.weight_size ? align_up(L->sub.weight_size(L->sub.user)) : 0;
+        char* slots = base + w.custom_slots;
+        void* sub_ws = base + w.custom_ws;
+        INFMOE_CUDA_TRY(cudaEventRecord(L->ev_fork, stream));
+        for (auto cs : L->copy_streams) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_fork, 0));
+        long long row0 = 0;
+        size_t j = 0;
+        for (int e = 0; e < L->E; ++e) {
+            const int n = L->h_count[e];
+            if (n == 0) continue;
+            const int slot = (int)(j % (size_t)L->mc);
+            void* weights = slot_bytes ? slots + slot_bytes * (size_t)slot : nullptr;
+            if (slot_bytes && L->sub.copy_weights) {
+                cudaStream_t cs = L->copy_streams[j % L->copy_streams.size()];
+                if (j >= (size_t)L->mc) INFMOE_CUDA_TRY(cudaStreamWaitEvent(cs, L->ev_freed[slot], 0));
+                if (L->sub.copy_weights(L->sub.user, weights, e, cs) != 0) {
+                    set_error("sublayer %s: copy_weights failed for expert %d", L->sublayer_type.c_str(), e);
+                    return INFMOE_ERR_STATE;
+                }
+                INFMOE_CUDA_TRY(cudaEventRecord(L->ev_ready[slot], cs));
+                INFMOE_CUDA_TRY(cudaStreamWaitEvent(stream, L->ev_ready[slot], 0));
+            }
+            if (L->sub.run(L->sub.user, e, n, weights, routed + row0 * L->D, post + row0 * L->D, sub_ws, stream) != 0) {
+                set_error("sublayer %s: run failed for expert %d", L->sublayer_type.c_str(), e);
+                return INFMOE_ERR_STATE;
+            }
+            INFMOE_CUDA_TRY(cudaEventRecord(L->ev_freed[slot], stream));
+            row0 += n;
+            ++j;
+        }
     } else {
         // 3. scatter fused with the experts' LayerNorm and the TF32 split (:354-355, T5FFLayer.cc:99-103)
         const bool pack = uses_umma(L);   // the GEMM run_ffn picks
@@ -1249,6 +1355,20 @@ int infmoe_layer_stage_ms(infmoe_layer* L, float* ms, int32_t* calls) {
 
 int64_t infmoe_layer_kernel_launches(const infmoe_layer* L) {
     return L ? (int64_t)(g_kernel_launches - L->launches_at_create) : (int64_t)g_kernel_launches;
+}
+
+int infmoe_register_sublayer(const char* type_name, const infmoe_sublayer_vtable* vt) {
+    if (!type_name || !*type_name || !vt || !vt->run) {
+        set_error("register_sublayer: a type name and a run callback are required");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (strcmp(type_name, "T5_FF") == 0 || strcmp(type_name, "Identity") == 0) {
+        set_error("register_sublayer: %s is a built-in sublayer type", type_name);
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    std::lock_guard<std::mutex> lock(g_sublayer_mu);
+    sublayer_registry()[type_name] = *vt;
+    return INFMOE_OK;
 }
 
 int infmoe_layer_destroy(infmoe_layer* L) {

@@ -6,6 +6,7 @@
 #pragma once
 
 #include <array>
+#include <memory>
 #include <string>
 
 #include "infmoe_c.h"
@@ -53,11 +54,21 @@ class MoELayerPlugin : public nvinfer1::IPluginV2DynamicExt {
     infmoe_layer* layer() const { return mLayer; }
     int sequenceLength() const { return mSequenceLength; }
 
+    // One rank's share of an expert-parallel layer (INFMOE_EP_WORLD > 1): the layer object holding this rank's
+    // experts and its wrapper.  Shared by the clones of a plugin: the communicator is one per process.
+    struct Sharded {
+        infmoe_layer* local = nullptr;
+        infmoe_ep* ep = nullptr;
+        ~Sharded();
+    };
+
    private:
     std::string mLayerName, mNamespace;
-    infmoe_layer* mLayer = nullptr;
+    infmoe_layer* mLayer = nullptr;   // the whole layer's attributes; also the compute object when one GPU runs it
+    std::shared_ptr<Sharded> mSharded;
     int mEmbeddingSize = 0;
     int mSequenceLength = -1;  // learnt in configurePlugin, like the reference (MoELayerPlugin.cc:170-180)
+    int64_t mMaxTokens = 0;    // largest batch * seq_len configurePlugin announced
 };
 
 class MoELayerPluginCreator : public nvinfer1::IPluginCreator {

@@ -58,6 +58,9 @@ WORKLOADS: Dict[str, Workload] = {
     # same per-tile shapes as cpm2 (d_model, tokens per expert) with a quarter of the experts and half the
     # d_ff: small enough (2 GB of weights, still far beyond L2) to capture under a profiler
     "cpm2_profile": Workload("cpm2_profile", "cpm_2", 8, 4096, 5120, 2, 512, seed=1235),
+    # the row-wise kernels (routing, dispatch, scatter + LayerNorm) at exactly the shapes of cpm2 -- same tokens,
+    # d_model and expert count -- with a d_ff of 512, so that the whole layer holds 0.8 GB: for profiler captures
+    "cpm2_rows_profile": Workload("cpm2_rows_profile", "cpm_2", 32, 4096, 512, 8, 512, seed=1235),
     # skewed routing, stresses the grouped GEMM's load balance
     "base_layer_zipf": Workload("base_layer_zipf", "base_layer", 64, 1024, 4096, 16, 1024, seed=1236, zipf_s=1.1),
     # expert-parallel case (sharded over 2/4/8 GPUs)

@@ -101,7 +101,9 @@ def reference_weight_file(ref_root):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("INFMOE_REFERENCE") or
+                    os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))),
+                                 "reference"), help="the InfMoE checkout (default: a directory `reference` beside this repository)")
     args = ap.parse_args()
     np.savez(os.path.join(HERE, "kat.npz"), **kat_cases())
     if os.path.isdir(args.reference):

@@ -142,6 +142,29 @@ def test_npz_reader_rejects_bad_files(tmp_path):
     assert e.value.status == 4
 
 
+def _npy_member(header: str, payload: bytes = b"") -> bytes:
+    h = header.encode("latin1")
+    return b"\x93NUMPY\x01\x00" + len(h).to_bytes(2, "little") + h + payload
+
+
+@pytest.mark.parametrize("header", [
+    "{'descr': '<f4', 'fortran_order':     ",                                  # nothing after the colon
+    "{'descr': '<f4', 'fortran_order': False, 'shape': (8,  ",                  # shape never closed
+    "{'descr': '<f4'",                                                          # keys missing
+    "{'descr': '<f4', 'fortran_order': False, 'shape': (4611686018427387904, 16), }",   # element count overflows
+    "",
+])
+def test_npz_reader_survives_garbled_npy_headers(tmp_path, header):
+    """A malformed member header is a format error, not an exception through the C boundary."""
+    import zipfile
+    path = str(tmp_path / "bad.npz")
+    with zipfile.ZipFile(path, "w", zipfile.ZIP_STORED) as z:
+        z.writestr("0/layer_norm_weight.npy", _npy_member(header, b"\0" * 32))
+    with pytest.raises(capi.InfMoEError) as e:
+        _check_file(path, 1, 8, 16)
+    assert e.value.status == 5
+
+
 def test_reference_generated_weight_file(golden_dir, capfd):
     """A file written by the reference's own MoELayerConfig.generate_random_weight_file: its wo_weight is
     flagged fortran_order and must be taken as raw C-order bytes, as the reference's reader does."""

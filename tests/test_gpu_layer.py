@@ -257,6 +257,66 @@ def test_identity_sublayer_returns_input(torch_cuda):
     layer.terminate()
 
 
+@pytest.mark.parametrize("variant", ["default", "base_layer"])
+def test_registered_sublayer_is_driven_like_the_built_in_ones(torch_cuda, oracle, variant):
+    """A sublayer type registered through the C ABI (the reference's extension point is a class derived from
+    MoESubLayer, plugin/sublayers/SubLayer.h:18-48): expert e scales its rows by a weight that the layer fetches
+    into one of max_concurrency device slots before every run.  Routing, dispatch and combine are the layer's."""
+    import ctypes
+    from infmoe_b200 import MoELayer, capi
+    torch = torch_cuda
+    E, D, T, mc = 7, 96, 333, 2
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((T, D)).astype(np.float32)
+    c = (rng.standard_normal((E, D)) * 0.1).astype(np.float32)
+    scales = np.arange(E, dtype=np.float32) + 2.0
+    # The fetch goes through the CUDA runtime directly: a torch copy from page-locked memory would make torch's host
+    # allocator remember the layer's copy stream, which no longer exists when the test's tensors are freed.
+    cudart = ctypes.CDLL("libcudart.so.12")
+    cudart.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    calls = {"init": 0, "copy": [], "run": []}
+
+    def tensor_at(ptr, n):
+        class V:
+            __cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+        return torch.as_tensor(V(), device="cuda")
+
+    def initialize(user, e, d, f, path):
+        calls["init"] += 1
+        return 0 if (e, d) == (E, D) else 1
+
+    def copy_weights(user, dst, expert, stream):
+        calls["copy"].append(int(expert))
+        return cudart.cudaMemcpyAsync(dst, scales[expert:expert + 1].ctypes.data, 4, 1, stream)   # 1: host to device
+
+    def run(user, expert, n, weights, src, dst, ws, stream):
+        calls["run"].append((int(expert), int(n)))
+        with torch.cuda.stream(torch.cuda.ExternalStream(int(stream or 0))):
+            torch.mul(tensor_at(src, n * D), tensor_at(weights, 1), out=tensor_at(dst, n * D))
+        return 0
+
+    vt = capi.SublayerVtable(None, capi.SUB_INIT_FN(initialize), capi.SUB_WEIGHT_SIZE_FN(lambda user: 4),
+                             capi.SUB_WS_SIZE_FN(lambda user, n: 0), capi.SUB_COPY_FN(copy_weights), capi.SUB_RUN_FN(run))
+    capi.check(capi.lib().infmoe_register_sublayer(b"ScaleByExpert", ctypes.byref(vt)))
+    layer = MoELayer.create(E, D, 4 * D, mc, c, None, "ScaleByExpert", variant, None)
+    with pytest.raises(capi.InfMoEError):
+        layer.forward_host(x)                       # not initialized yet
+    layer.initialize()
+    out = layer.forward_host(x)
+    gate, score = oracle.route(x, c, None)
+    want = x * (gate[:, None].astype(np.float32) + 2.0)
+    if variant == "base_layer":
+        alpha = (1.0 / (1.0 + np.exp(-score.astype(np.float64))))[:, None]
+        want = alpha * want + (1 - alpha) * x
+    np.testing.assert_allclose(out, want, rtol=2e-6, atol=1e-6)
+    active = sorted(set(int(e) for e in gate))
+    assert calls["init"] == 1 and calls["copy"] == active
+    assert calls["run"] == [(e, int(np.count_nonzero(gate == e))) for e in active]
+    layer.terminate()
+    with pytest.raises(capi.InfMoEError):
+        MoELayer.create(E, D, 4 * D, mc, c, None, "NoSuchSublayer", variant, None)
+
+
 def test_nan_input_is_reported_not_trapped(torch_cuda):
     from infmoe_b200 import MoELayer, capi, synth
     w = synth.scaled(synth.WORKLOADS["tiny_default"])

@@ -45,3 +45,59 @@ def test_plugin_enqueue_matches_binding_and_oracle(oracle, tmp_path):
     layer.terminate()
     L.trtmoe_plugin_delete(clone)
     L.trtmoe_plugin_delete(p)
+
+
+def _ep_plugin_worker(rank, world, id_file, npz, variant, ret):
+    import os
+    os.environ.update(INFMOE_EP_WORLD=str(world), INFMOE_EP_RANK=str(rank), INFMOE_EP_ID_FILE=id_file,
+                      NCCL_NVLS_ENABLE="0")
+    import torch
+    torch.cuda.set_device(rank)
+    from infmoe_b200 import synth
+    from tests import plugin_util as pu
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=8, embedding_size=128, hidden_size=256,
+                     batch=4, seq_len=50)
+    x, c, ln = synth.gen_inputs(w)
+    arr, n, keep = pu.make_fields(expert_count=8, embedding_size=128, hidden_size=256, max_concurrency=2,
+                                  expert_centroids=c, expert_weight_file=npz, expert_sublayer_type="T5_FF",
+                                  moe_variant=variant, layernorm_weight=ln)
+    L = pu.lib()
+    p = L.trtmoe_create_plugin(L.trtmoe_get_creator(b"MoELayerPlugin", b"1"), b"moe", arr, n)
+    assert p
+    b = w.batch // world                                   # every rank runs its own batch items
+    L.trtmoe_plugin_configure(p, b, w.seq_len, w.embedding_size)
+    assert L.trtmoe_plugin_initialize(p) == 0              # collective: loads this rank's experts, joins the others
+    clone = L.trtmoe_plugin_clone(p)
+    rows = x.reshape(w.batch, w.seq_len, -1)[rank * b:(rank + 1) * b].reshape(-1, w.embedding_size)
+    dx = torch.from_numpy(np.ascontiguousarray(rows)).cuda()
+    out = torch.empty_like(dx)
+    ws = torch.empty(max(L.trtmoe_plugin_workspace(p, b, w.seq_len, w.embedding_size), 16), dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.trtmoe_plugin_enqueue(clone, b, w.seq_len, w.embedding_size, dx.data_ptr(), out.data_ptr(), ws.data_ptr(), s) == 0
+    torch.cuda.synchronize()
+    ret[rank] = out.cpu().numpy()
+    L.trtmoe_plugin_delete(clone)
+    L.trtmoe_plugin_delete(p)
+
+
+@pytest.mark.parametrize("variant", ["cpm_2", "base_layer"])
+def test_plugin_runs_expert_parallel_on_two_gpus(oracle, tmp_path, variant):
+    """The C++ plugin classes with INFMOE_EP_WORLD=2: each process creates the plugin from the WHOLE layer's
+    attributes, as TensorRT would on every rank, and enqueue() goes through infmoe_ep_forward."""
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from infmoe_b200 import MoELayer, synth
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=8, embedding_size=128, hidden_size=256,
+                     batch=4, seq_len=50)
+    x, c, ln = synth.gen_inputs(w)
+    npz = synth.write_npz(w, str(tmp_path / "w.npz"))
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_ep_plugin_worker, args=(2, str(tmp_path / "ep.id"), npz, variant, ret), nprocs=2, join=True)
+        out = np.concatenate([ret[0], ret[1]])
+    single = MoELayer.create(8, 128, 256, 2, c, npz, "T5_FF", variant, ln)
+    single.initialize()
+    np.testing.assert_array_equal(out, single.forward_host(x))
+    single.terminate()
