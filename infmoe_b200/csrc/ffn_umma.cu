@@ -603,40 +603,48 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                        ? args.out_row_ptr[lane_row]
                                        : (unsigned long long)(args.out_hi + (size_t)lane_row * (size_t)args.M_total);
                 }
+                if (EPI == EPI_GELU_PAIR) {
+                    // Even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index f, so a lane pair holds
+                    // (a, b) of f for all 16 token columns.  The pair splits the columns: the even lane takes the
+                    // even ones, the odd lane the odd ones; one shuffle per column pair hands each lane the half
+                    // it lacks, and every gelu is evaluated once.
+                    const int F = args.M_total >> 1, f = m >> 1;
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int c = 0; c < 16; c += 2) {
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? sum[i][c] : sum[i][c + 1], 1);
+                        const float a = odd ? got : sum[i][c], b = odd ? sum[i][c + 1] : got;
+                        const float g = gelu_dot_fast(a, b);
+                        const uint32_t hb = (__float_as_uint(g) + 0x1000u) & 0xffffe000u;   // TF32 head, as split_tf32
+                        const float hi = __uint_as_float(hb), lo = __fsub_rn(g, hi);
+                        const int col = sl * 16 + c + (odd ? 1 : 0);
+                        // head plane, and the packed plane, which is zero padded to whole groups of 32 (weight rows
+                        // past the matrix are zero in the tiled layout, so those values are 0)
+                        if (col < t.n_tok) {
+                            if (f < F) args.out_hi[(size_t)(t.row0 + col) * (size_t)F + (size_t)f] = hi;
+                            if (f < ((F + 31) & ~31)) {
+                                uint16_t* gp = reinterpret_cast<uint16_t*>(args.out_lo) +
+                                               (size_t)(t.row0 + col) * pack_pitch(F) + (size_t)(f >> 5) * 64 + (f & 31);
+                                const uint32_t hl = pack_bf16x2(hi, lo);
+                                gp[0] = (uint16_t)(hl & 0xffffu);
+                                gp[32] = (uint16_t)(hl >> 16);
+                            }
+                        }
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const int col = sl * 16 + c;
                     const float v = sum[i][c];
-                    const unsigned long long out_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_ptr, c) : 0ull;
-                    const float alpha = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_alpha, c) : 0.f;
-                    const int resid_row = EPI == EPI_RESIDUAL ? __shfl_sync(0xffffffffu, lane_row, c) : 0;
-                    if (EPI == EPI_GELU_PAIR) {
-                        // even weight row = wi_0 (a), odd row = wi_1 (b) of the same d_ff index
-                        const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-                        const float a = (lane & 1) ? other : v, b = (lane & 1) ? v : other;
-                        float hi, lo;
-                        split_tf32(gelu_dot(a, b), hi, lo);
-                        // even lane: head plane; odd lane: packed plane, which is zero padded to whole groups of
-                        // 32 (weight rows past the matrix are zero in the tiled layout, so those values are 0)
-                        const int F = args.M_total >> 1, f = m >> 1;
-                        if (col < t.n_tok) {
-                            if (!(lane & 1)) {
-                                if (m_ok) args.out_hi[(size_t)(t.row0 + col) * (size_t)F + (size_t)f] = hi;
-                            } else if (f < ((F + 31) & ~31)) {
-                                uint16_t* g = reinterpret_cast<uint16_t*>(args.out_lo) +
-                                              (size_t)(t.row0 + col) * pack_pitch(F) + (size_t)(f >> 5) * 64 + (f & 31);
-                                const uint32_t hl = pack_bf16x2(hi, lo);
-                                g[0] = (uint16_t)(hl & 0xffffu);
-                                g[32] = (uint16_t)(hl >> 16);
-                            }
-                        }
-                    } else {
-                        if (col < t.n_tok && m_ok) {
-                            const float x = args.resid[(size_t)resid_row * (size_t)args.M_total + (size_t)m];
-                            float y = __fadd_rn(x, v);
-                            if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
-                            reinterpret_cast<float*>(out_row)[m] = y;
-                        }
+                    const unsigned long long out_row = __shfl_sync(0xffffffffu, lane_ptr, c);
+                    const float alpha = __shfl_sync(0xffffffffu, lane_alpha, c);
+                    const int resid_row = __shfl_sync(0xffffffffu, lane_row, c);
+                    if (col < t.n_tok && m_ok) {
+                        const float x = args.resid[(size_t)resid_row * (size_t)args.M_total + (size_t)m];
+                        float y = __fadd_rn(x, v);
+                        if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
+                        reinterpret_cast<float*>(out_row)[m] = y;
                     }
                 }
             }
