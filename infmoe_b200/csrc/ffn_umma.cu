@@ -284,11 +284,15 @@ struct GemmArgs {
 };
 
 // True when k block kb (of KB) of a tile is the last one of a chunk of its accumulator (each accumulator
-// takes every other k block).  Chunks are CHUNK_BLOCKS own blocks long; those of the odd k blocks are shifted
-// by half a chunk so that the two accumulators are not drained at the same time.
+// takes every other k block).  Chunks are CHUNK_BLOCKS own blocks long, except the first one of a tile, which
+// is 12 blocks for the even and 16 for the odd k blocks: the accumulate warps are still busy with the previous
+// tile's epilogue when a tile starts, and an accumulator that needs draining before they are back stalls its
+// MMA issuer.  The different first lengths also keep the two accumulators half a chunk apart, so that they
+// are never drained at the same time.
 __device__ __forceinline__ bool chunk_ends(int kb, int KB) {
-    const int i = kb & 1, n = kb >> 1;
-    return ((n + 1 + i * (CHUNK_BLOCKS / 2)) % CHUNK_BLOCKS) == 0 || kb + 2 >= KB;
+    const int first = (kb & 1) ? 2 * CHUNK_BLOCKS : CHUNK_BLOCKS + CHUNK_BLOCKS / 2;
+    const int done = (kb >> 1) + 1 - first;      // own blocks past the first chunk, counting this one
+    return (done >= 0 && done % CHUNK_BLOCKS == 0) || kb + 2 >= KB;
 }
 
 // Tensor maps of the two token planes, one per box height 16, 32, ... 160 rows: a tile's load fetches exactly
@@ -618,16 +622,19 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         const uint32_t hb = (__float_as_uint(g) + 0x1000u) & 0xffffe000u;   // TF32 head, as split_tf32
                         const float hi = __uint_as_float(hb), lo = __fsub_rn(g, hi);
                         const int col = sl * 16 + c + (odd ? 1 : 0);
-                        // head plane, and the packed plane, which is zero padded to whole groups of 32 (weight rows
-                        // past the matrix are zero in the tiled layout, so those values are 0)
+                        // Packed plane: neighbouring f (lanes two apart, same column) exchange their halves so that
+                        // every lane stores one 32-bit word, even f the pair of heads, odd f the pair of tails.
+                        const uint32_t hl = pack_bf16x2(hi, lo);
+                        const uint32_t nb = __shfl_xor_sync(0xffffffffu, hl, 2);
+                        // The packed plane is zero padded to whole groups of 32 (weight rows past the matrix are
+                        // zero in the tiled layout, so those values are 0).
                         if (col < t.n_tok) {
                             if (f < F) args.out_hi[(size_t)(t.row0 + col) * (size_t)F + (size_t)f] = hi;
                             if (f < ((F + 31) & ~31)) {
                                 uint16_t* gp = reinterpret_cast<uint16_t*>(args.out_lo) +
                                                (size_t)(t.row0 + col) * pack_pitch(F) + (size_t)(f >> 5) * 64 + (f & 31);
-                                const uint32_t hl = pack_bf16x2(hi, lo);
-                                gp[0] = (uint16_t)(hl & 0xffffu);
-                                gp[32] = (uint16_t)(hl >> 16);
+                                if (!(f & 1)) *reinterpret_cast<uint32_t*>(gp) = (hl & 0xffffu) | (nb << 16);
+                                else *reinterpret_cast<uint32_t*>(gp + 31) = (nb >> 16) | (hl & 0xffff0000u);
                             }
                         }
                     }
