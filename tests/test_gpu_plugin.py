@@ -58,9 +58,10 @@ def _ep_plugin_worker(rank, world, id_file, npz, variant, ret):
     w = synth.scaled(synth.WORKLOADS["cpm2"], variant=variant, expert_count=8, embedding_size=128, hidden_size=256,
                      batch=4, seq_len=50)
     x, c, ln = synth.gen_inputs(w)
+    extra = {} if ln is None else {"layernorm_weight": ln}       # only cpm_2 has a pre-gating LayerNorm
     arr, n, keep = pu.make_fields(expert_count=8, embedding_size=128, hidden_size=256, max_concurrency=2,
                                   expert_centroids=c, expert_weight_file=npz, expert_sublayer_type="T5_FF",
-                                  moe_variant=variant, layernorm_weight=ln)
+                                  moe_variant=variant, **extra)
     L = pu.lib()
     p = L.trtmoe_create_plugin(L.trtmoe_get_creator(b"MoELayerPlugin", b"1"), b"moe", arr, n)
     assert p
