@@ -640,16 +640,24 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     }
                     continue;
                 }
+                // The residual values of the slice's 16 columns are fetched first, all in flight together: issued
+                // one by one between the stores (which may alias them as far as the compiler knows) each would
+                // cost a trip to L2 or HBM, 80 in a row per thread, and the next tile's first chunk would wait.
+                float xres[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int resid_row = __shfl_sync(0xffffffffu, lane_row, c);
+                    xres[c] = (sl * 16 + c < t.n_tok && m_ok)
+                                  ? args.resid[(size_t)resid_row * (size_t)args.M_total + (size_t)m] : 0.f;
+                }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const int col = sl * 16 + c;
-                    const float v = sum[i][c];
                     const unsigned long long out_row = __shfl_sync(0xffffffffu, lane_ptr, c);
                     const float alpha = __shfl_sync(0xffffffffu, lane_alpha, c);
-                    const int resid_row = __shfl_sync(0xffffffffu, lane_row, c);
                     if (col < t.n_tok && m_ok) {
-                        const float x = args.resid[(size_t)resid_row * (size_t)args.M_total + (size_t)m];
-                        float y = __fadd_rn(x, v);
+                        const float x = xres[c];
+                        float y = __fadd_rn(x, sum[i][c]);
                         if (args.mix_score) y = mix_value(alpha, 1.0f - alpha, y, x);
                         reinterpret_cast<float*>(out_row)[m] = y;
                     }
