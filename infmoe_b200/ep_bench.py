@@ -169,6 +169,14 @@ def _measure(total, scaling, steps, warmup, torch, dist, dev, rank, world, peaks
 
     cnt_p, _, _, _ = ep.received()
     received = int(read_device(cnt_p, world, np.int32).sum())
+    # every rank's share of the step: the rank that takes longest over its experts keeps the others waiting
+    mine = torch.tensor([phase_ms.get("experts", 0.0), phase_ms.get("wait_results", 0.0), stage_ms["ffn_gemm1"],
+                         stage_ms["ffn_gemm2"], float(received), float(clocks.summary().get("sm_mhz") or 0.0)],
+                        device=dev, dtype=torch.float32)
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    per_rank = {k: [round(float(t[i].item()), 3) for t in every]
+                for i, k in enumerate(("experts_ms", "wait_results_ms", "gemm1_ms", "gemm2_ms", "rows_received", "sm_mhz"))}
     result = None
     if rank == 0:
         gate = read_device(ep.last_routing()[0], T_local, np.int32)
@@ -183,7 +191,7 @@ def _measure(total, scaling, steps, warmup, torch, dist, dev, rank, world, peaks
             roofline["traffic"] = None
         result = {"ms": float(ms.item()), "tokens": T_local * world, "tokens_per_gpu": T_local, "experts_per_gpu": per,
                   "launches": int(launches.item()), "stage_ms_rank0": stage_ms, "phase_ms_rank0": phase_ms,
-                  "rows_received_rank0": received, "roofline": roofline, "clocks": clock_summary, "parity": parity,
+                  "rows_received_rank0": received, "per_rank": per_rank, "roofline": roofline, "clocks": clock_summary, "parity": parity,
                   "e2e": e2e, "hx_bytes": int(hx.numel() * 4)}
     dist.barrier()
     ep.destroy()
@@ -248,7 +256,7 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
                     "same_bits_as_device_path": e2e["same_bits_as_device_path"], "host_placement_rank0": numa},
             "gpu_launches": main["launches"], "stage_ms_rank0": main["stage_ms_rank0"],
             "phase_ms_rank0": main["phase_ms_rank0"], "rows_received_rank0": main["rows_received_rank0"],
-            "parity": main["parity"], "roofline": main["roofline"], "cpu_baseline": None, "clocks": main["clocks"],
+            "per_rank": main["per_rank"], "parity": main["parity"], "roofline": main["roofline"], "cpu_baseline": None, "clocks": main["clocks"],
             "ep_cpm2": extra,
         }
         print(json.dumps(line), flush=True)
