@@ -36,7 +36,7 @@ def _local_layers(w, world, c, experts=None, device_experts=False):
     return layers
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("variant", ["cpm_2", "base_layer", "default"])
 def test_loopback_ranks_match_single_gpu_and_oracle(oracle, variant, world):
     import torch
@@ -48,7 +48,8 @@ def test_loopback_ranks_match_single_gpu_and_oracle(oracle, variant, world):
     x, c, ln = synth.gen_inputs(w)
     experts = [synth.gen_expert_numpy(w, e) for e in range(w.expert_count)]
     # ranks bring different numbers of tokens (one of them a single token)
-    bounds = [0, 301, w.tokens] if world == 2 else [0, 1, 300, 301, w.tokens]
+    bounds = {2: [0, 301, w.tokens], 4: [0, 1, 300, 301, w.tokens],
+              8: [0, 1, 100, 101, 200, 301, 400, 401, w.tokens]}[world]     # at eight ranks: one expert per rank
     locals_ = _local_layers(w, world, c, experts)
     eps = NativeExpertParallel.create_loopback(locals_, c, ln, variant, max_tokens=400)
     xs = [torch.from_numpy(x[bounds[r]:bounds[r + 1]].copy()).cuda() for r in range(world)]
