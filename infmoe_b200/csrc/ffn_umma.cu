@@ -872,6 +872,12 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int* status, unsi
 
 }  // namespace
 
+// Tensor map over a row-major FP32 matrix [rows][K] with boxes of 32 floats x box_rows rows and the 128-byte swizzle
+// (for the other kernels of the library; K * 4 and the base address must be multiples of 16 bytes).
+int make_f32_row_map(CUtensorMap* map, const void* base, long long K, long long rows, int box_rows) {
+    return make_map(map, base, (uint64_t)K, (uint64_t)rows, 1, box_rows, 2);
+}
+
 int launch_wait_probe(unsigned long long limit_ns, int* status, unsigned long long* waited_ns, cudaStream_t stream) {
     wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, status, waited_ns);
     note_launch();

@@ -1,6 +1,7 @@
 // Launchers of the CUDA kernels (defined in route.cu, dispatch.cu, rows.cu, ffn_simt.cu, ffn_umma.cu).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -9,6 +10,7 @@ namespace infmoe {
 
 int launch_route(const float* X, const float* C, const float* gamma, long long T, int D, int E, int* gate,
                  float* score, int* status, cudaStream_t stream);
+int make_f32_row_map(CUtensorMap* map, const void* base, long long K, long long rows, int box_rows);
 int launch_select_top1(long long T, int E, const float* aff, int* gate, float* weight, int* status,
                        cudaStream_t stream);
 // region_count != NULL: the T slots are regions of region_size slots, of which only the first region_count[s]

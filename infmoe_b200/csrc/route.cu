@@ -18,7 +18,7 @@
 // step of the row a thread reads 8 token values and 8 centroid values (one 128-bit shared-memory
 // load each, every load shared by four lanes) for 256 fused multiply-adds, so neither the
 // shared-memory pipe nor the instruction issue limits the FP32 pipe.  Rows and centroids are
-// staged through shared memory with cp.async, 256 floats per row and stage, double buffered; the
+// staged through shared memory with cp.async, 256 floats per row and stage, three buffers; the
 // LayerNorm is applied once per staged value, in place, by the thread that fetched it.  After the
 // last stage the partial sums of l and l + 16 are combined by a shuffle (the butterfly's first
 // step), the other 16 go through shared memory, and a warp per token finishes the butterfly and
@@ -27,7 +27,13 @@
 // Shared-memory tiles: [stage][step][row][slot] of 16-byte chunks, slot = l ^ (row & 3) ^ (4 if
 // l >= 16): consecutive l of one row fill one 512-byte line (conflict-free staging), and the eight
 // chunks a warp reads at once (4 rows x 2 values of l) fall into eight different bank groups.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
+#include "kernels.h"
 
 namespace infmoe {
 
@@ -43,14 +49,14 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int RT_TOKENS = 32;       // tokens per CTA
 constexpr int RT_EXPERTS = 32;      // experts per pass
-constexpr int RT_THREADS = 512;
+constexpr int RT_THREADS = 256;
 constexpr int RT_STEPS = 2;         // 128-float steps per stage
 constexpr int RT_STAGE_FLOATS = RT_STEPS * 128;
-constexpr int RT_STAGES = 2;
+constexpr int RT_STAGES = 3;
 constexpr int RT_TILE_CHUNKS = RT_STEPS * 32 * 32;             // 16-byte chunks of one tile (tokens or experts) of one stage
 constexpr int RT_SMEM = RT_STAGES * 2 * RT_TILE_CHUNKS * 16;   // token and centroid tiles
 constexpr int RT_RED_PITCH = 36;    // floats per token row of the partial-sum buffer (32 experts + padding)
-static_assert(16 * RT_TOKENS * RT_RED_PITCH * 4 <= RT_SMEM, "the partial sums reuse the tile memory");
+static_assert(8 * RT_TOKENS * RT_RED_PITCH * 4 <= RT_SMEM, "the partial sums reuse the tile memory");
 
 __device__ __forceinline__ int rt_slot(int l, int row) { return l ^ (row & 3) ^ ((l >> 4) << 2); }
 
@@ -105,43 +111,47 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
     extern __shared__ __align__(16) unsigned char rt_smem[];
     float4* const xs = reinterpret_cast<float4*>(rt_smem);          // [stage][step][token][slot]
     float4* const cs = xs + RT_STAGES * RT_TILE_CHUNKS;             // [stage][step][expert][slot]
-    float* const red = reinterpret_cast<float*>(rt_smem);           // [16][token][RT_RED_PITCH], after the last stage
+    float* const red = reinterpret_cast<float*>(rt_smem);           // [8][token][RT_RED_PITCH], after the last stage
     __shared__ float s_mean[RT_TOKENS], s_rstd[RT_TOKENS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long t0 = (long long)blockIdx.x * RT_TOKENS;
     const bool use_ln = gamma != nullptr;
-
-    // row statistics, two tokens per warp (rows past the end alias the tile's first row)
+    // row statistics, four tokens per warp, two at a time (rows past the end alias the tile's first row)
     if (use_ln) {
-        float mean[2], rstd[2];
-        warp_two_row_stats<VEC>(X + (t0 + (t0 + warp < T ? warp : 0)) * (long long)D,
-                                X + (t0 + (t0 + warp + 16 < T ? warp + 16 : 0)) * (long long)D, D, mean, rstd);
-        if (lane == 0) {
-            s_mean[warp] = mean[0];
-            s_rstd[warp] = rstd[0];
-            s_mean[warp + 16] = mean[1];
-            s_rstd[warp + 16] = rstd[1];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const int ra = warp + 16 * p, rb = ra + 8;
+            float mean[2], rstd[2];
+            warp_two_row_stats<VEC>(X + (t0 + (t0 + ra < T ? ra : 0)) * (long long)D,
+                                    X + (t0 + (t0 + rb < T ? rb : 0)) * (long long)D, D, mean, rstd);
+            if (lane == 0) {
+                s_mean[ra] = mean[0];
+                s_rstd[ra] = rstd[0];
+                s_mean[rb] = mean[1];
+                s_rstd[rb] = rstd[1];
+            }
         }
     }
     __syncthreads();
 
-    // compute role: partial index l, 8 tokens tt + 4 j, 8 experts te + 4 jj
-    const int l = warp + 16 * (lane >> 4);
-    const int tt = (lane >> 2) & 3, te = lane & 3;
-    // staging role: chunk (step, l) of rows rg + 8 r, r = 0..3
-    const int st_step = (tid & 63) >> 5, st_l = tid & 31, rg = tid >> 6;
+    // compute role: partial index l = 8 (lane / 8) + warp, 16 tokens tt + 2 j, 8 experts te + 4 jj
+    const int l = 8 * (lane >> 3) + warp;
+    const int tt = (lane >> 2) & 1, te = lane & 3;
+    const int xslot0 = rt_slot(l, tt), xslot1 = rt_slot(l, tt + 2);   // rows tt + 2 j: j even / odd
+    const int cslot = rt_slot(l, te);
+    // staging role: chunk (step, l) of rows rg + 4 r, r = 0..7
+    const int st_step = (tid >> 5) & 1, st_l = tid & 31, rg = tid >> 6;
     const int st_k = st_step * 128 + st_l * 4;   // first float of my chunk inside a stage
 
     // stages of one pass over the row; tiles past the end of a row (or of the tokens / experts) are zero
     const int nstages = (D + RT_STAGE_FLOATS - 1) / RT_STAGE_FLOATS;
-    auto issue = [&](int stage, int e0) {
-        const int buf = stage & 1;
+    auto issue = [&](int stage, int buf, int e0) {
         const int k = stage * RT_STAGE_FLOATS + st_k;
         float4* xt = xs + (buf * RT_STEPS + st_step) * 1024;
         float4* ct = cs + (buf * RT_STEPS + st_step) * 1024;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int row = rg + 8 * r;
+        for (int r = 0; r < 8; ++r) {
+            const int row = rg + 4 * r;
             float4* xd = xt + row * 32 + rt_slot(st_l, row);
             float4* cd = ct + row * 32 + rt_slot(st_l, row);
             const bool x_ok = t0 + row < T && k < D, c_ok = e0 + row < E && k < D;
@@ -161,14 +171,13 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         const int k = stage * RT_STAGE_FLOATS + st_k;
         return (use_ln && k < D) ? load_row4(gamma, k, D, VEC) : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    auto normalise = [&](int stage, const float4& g) {
-        const int buf = stage & 1;
+    auto normalise = [&](int stage, int buf, const float4& g) {
         const int k = stage * RT_STAGE_FLOATS + st_k;
         if (k >= D) return;
         float4* xt = xs + (buf * RT_STEPS + st_step) * 1024;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int row = rg + 8 * r;
+        for (int r = 0; r < 8; ++r) {
+            const int row = rg + 4 * r;
             if (t0 + row >= T) continue;
             float4* xd = xt + row * 32 + rt_slot(st_l, row);
             float4 v = *xd;
@@ -181,26 +190,33 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
         }
     };
 
-    float best[2] = {-FLT_MAX, -FLT_MAX};   // reference plugin/cuda/moe.cu:26-27; tokens warp and warp + 16
-    int best_e[2] = {-1, -1};
+    float best[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};   // reference plugin/cuda/moe.cu:26-27; tokens warp + 8 q
+    int best_e[4] = {-1, -1, -1, -1};
 
     for (int e0 = 0; e0 < E; e0 += RT_EXPERTS) {
-        float acc[8][8];
+        float acc[16][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 16; ++j)
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) acc[j][jj] = 0.f;
 
-        issue(0, e0);
+        // Three buffers.  While the warps of a CTA multiply stage s, each of them, when it is done, waits for its own
+        // copies of stage s + 1 and normalises them, so that this work overlaps the other warps' multiply-adds
+        // instead of standing between two barriers; the copies of stage s + 2 go out before the multiply-adds.
+        issue(0, 0, e0);
         cp_async_commit();
-        for (int stage = 0; stage < nstages; ++stage) {
-            const float4 g = load_gamma(stage);   // in flight while the copies below are issued and awaited
-            if (stage + 1 < nstages) issue(stage + 1, e0);
+        if (nstages > 1) issue(1, 1, e0);
+        cp_async_commit();
+        float4 g = load_gamma(0);
+        cp_async_wait<1>();              // this thread's copies of stage 0 have landed
+        if (use_ln) normalise(0, 0, g);
+        g = load_gamma(1);
+        __syncthreads();
+        for (int stage = 0, buf = 0; stage < nstages; ++stage, buf = buf == RT_STAGES - 1 ? 0 : buf + 1) {
+            const int next = buf == RT_STAGES - 1 ? 0 : buf + 1, after = next == RT_STAGES - 1 ? 0 : next + 1;
+            // buffer `after` was read in stage - 1, which every thread left before the barrier that ended it
+            if (stage + 2 < nstages) issue(stage + 2, after, e0);
             cp_async_commit();
-            cp_async_wait<1>();          // this thread's copies of `stage` have landed
-            if (use_ln) normalise(stage, g);
-            __syncthreads();             // ... and everybody else's
-            const int buf = stage & 1;
 #pragma unroll
             for (int step = 0; step < RT_STEPS; ++step) {
                 if (stage * RT_STAGE_FLOATS + step * 128 >= D) break;
@@ -208,14 +224,10 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
                 const float4* ct = cs + (buf * RT_STEPS + step) * 1024;
                 float4 c[8];
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                    const int row = te + 4 * jj;
-                    c[jj] = ct[row * 32 + rt_slot(l, row)];
-                }
+                for (int jj = 0; jj < 8; ++jj) c[jj] = ct[(te + 4 * jj) * 32 + cslot];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int row = tt + 4 * j;
-                    const float4 x = xt[row * 32 + rt_slot(l, row)];
+                for (int j = 0; j < 16; ++j) {
+                    const float4 x = xt[(tt + 2 * j) * 32 + ((j & 1) ? xslot1 : xslot0)];
                     // Elements past the end of a row are zero in both tiles: their products are exact zeros and
                     // leave the partial sums' bits unchanged, so they need no predicate.
 #pragma unroll
@@ -228,32 +240,39 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
                     for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.w, c[jj].w, acc[j][jj]);
                 }
             }
-            __syncthreads();             // everyone is done with this stage's tiles before they are refilled
+            if (stage + 1 < nstages) {
+                cp_async_wait<1>();      // this thread's copies of stage + 1 have landed
+                if (use_ln) normalise(stage + 1, next, g);
+                g = load_gamma(stage + 2);
+            }
+            __syncthreads();             // stage + 1 is complete for everybody; everybody is done with `stage`
         }
-
-        // butterfly, first step (xor 16 over l): the two halves of the warp hold l and l + 16 of the same pairs
+        // butterfly, first two steps (xor 16 and xor 8 over l): the four quarters of the warp hold l, l + 8, l + 16
+        // and l + 24 of the same (token, expert) pairs
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 16; ++j)
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj)
+            for (int jj = 0; jj < 8; ++jj) {
                 acc[j][jj] = __fadd_rn(acc[j][jj], __shfl_xor_sync(0xffffffffu, acc[j][jj], 16));
-        if (lane < 16) {
+                acc[j][jj] = __fadd_rn(acc[j][jj], __shfl_xor_sync(0xffffffffu, acc[j][jj], 8));
+            }
+        if (lane < 8) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 16; ++j)
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj)
-                    red[(warp * RT_TOKENS + tt + 4 * j) * RT_RED_PITCH + te + 4 * jj] = acc[j][jj];
+                    red[(warp * RT_TOKENS + tt + 2 * j) * RT_RED_PITCH + te + 4 * jj] = acc[j][jj];
         }
         __syncthreads();
-        // steps xor 8, 4, 2, 1 and the argmax: warp -> tokens warp and warp + 16, lane -> expert e0 + lane
+        // steps xor 4, 2, 1 and the argmax: warp -> tokens warp + 8 q, lane -> expert e0 + lane
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int t = warp + 16 * q;
-            float v[16];
+        for (int q = 0; q < 4; ++q) {
+            const int t = warp + 8 * q;
+            float v[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = red[(i * RT_TOKENS + t) * RT_RED_PITCH + lane];
+            for (int i = 0; i < 8; ++i) v[i] = red[(i * RT_TOKENS + t) * RT_RED_PITCH + lane];
 #pragma unroll
-            for (int off = 8; off >= 1; off >>= 1)
+            for (int off = 4; off >= 1; off >>= 1)
 #pragma unroll
                 for (int i = 0; i < off; ++i) v[i] = __fadd_rn(v[i], v[i + off]);
             // Candidates of this pass have higher indices than the running winner, so they replace it only when
@@ -279,8 +298,271 @@ route_kernel(const float* __restrict__ X, const float* __restrict__ C, const flo
     }
     if (lane == 0) {
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const long long t = t0 + warp + 16 * q;
+        for (int q = 0; q < 4; ++q) {
+            const long long t = t0 + warp + 8 * q;
+            if (t >= T) continue;
+            gate[t] = best_e[q];
+            if (score) score[t] = best[q];
+            if (best_e[q] < 0 && status) atomicOr(status, STATUS_NO_EXPERT);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel with the tiles fetched by TMA.  Issuing 4096 16-byte cp.async copies per stage costs the CTA about
+// 1500 cycles of its load/store pipe, as much as half of the multiply-adds of the stage; one thread issuing 16
+// tensor copies (boxes of 32 floats x 32 rows, eight per tile) costs nothing.  Rows past the tokens, the experts or
+// the end of a row are zero-filled by the copy.  The 128-byte swizzle of the copy takes the place of rt_slot: 16-byte
+// chunk c of row r of a box sits at chunk c ^ (r & 7), which keeps both the normalising and the multiplying reads
+// (rows r, r + 1 or r .. r + 3 within a quarter warp) free of bank conflicts.  The partial sums of all 32 values of
+// l go through shared memory (the three stage buffers leave room for them), which replaces 256 shuffles per thread.
+// Needs 16-byte aligned rows (D % 4 == 0); other shapes take route_kernel.
+__device__ __forceinline__ uint32_t rt_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long rt_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool rt_mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up (and tells the other threads to) two seconds after it started.
+__device__ __forceinline__ bool rt_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (rt_mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = rt_global_ns();
+    while (true) {
+        for (int i = 0; i < 64; ++i)
+            if (rt_mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (rt_global_ns() - t0 > 2000000000ull) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void rt_tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+constexpr int RT_RED_L = 1153;      // floats between the partial sums of l and l + 1 (odd: conflict-free stores)
+static_assert(32 * RT_RED_L * 4 <= RT_SMEM, "the partial sums reuse the tile memory");
+// float4 index of chunk l of row `row` in the tile of one stage (boxes: [step][l / 8][row][8 chunks])
+__device__ __forceinline__ int rt_box_idx(int step, int l, int row) {
+    return ((step * 4 + (l >> 3)) * 32 + row) * 8 + ((l & 7) ^ (row & 7));
+}
+
+__global__ void __launch_bounds__(RT_THREADS, 1)
+route_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
+                 const float* __restrict__ X, const float* __restrict__ gamma, long long T, int D, int E,
+                 int* __restrict__ gate, float* __restrict__ score, int* __restrict__ status) {
+    extern __shared__ unsigned char rt_smem_raw[];
+    unsigned char* const rt_smem = rt_smem_raw + ((1024u - (rt_smem_u32(rt_smem_raw) & 1023u)) & 1023u);
+    float4* const xs = reinterpret_cast<float4*>(rt_smem);          // [buffer][step][box][token][chunk]
+    float4* const cs = xs + RT_STAGES * RT_TILE_CHUNKS;             // [buffer][step][box][expert][chunk]
+    float* const red = reinterpret_cast<float*>(rt_smem);           // [l][token][RT_RED_PITCH] at pitch RT_RED_L
+    __shared__ float s_mean[RT_TOKENS], s_rstd[RT_TOKENS];
+    __shared__ __align__(8) uint64_t s_full[RT_STAGES];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long t0 = (long long)blockIdx.x * RT_TOKENS;
+    const bool use_ln = gamma != nullptr;
+    volatile int* abort_flag = &s_abort;
+
+    const int nstages = (D + RT_STAGE_FLOATS - 1) / RT_STAGE_FLOATS;
+    const uint32_t xs_addr = rt_smem_u32(xs), cs_addr = rt_smem_u32(cs);
+    // one thread: the 16 copies of a stage (gs counts the stages of all passes; buffer and barrier gs % RT_STAGES)
+    auto issue = [&](uint32_t gs, int stage, int e0) {
+        const uint32_t buf = gs % RT_STAGES, bar = rt_smem_u32(&s_full[buf]);
+        // the buffer was last touched by ordinary loads and stores; order them before the copies' writes
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * RT_TILE_CHUNKS * 16u)
+                     : "memory");
+#pragma unroll
+        for (int b = 0; b < RT_STEPS * 4; ++b) {
+            const int k0 = stage * RT_STAGE_FLOATS + b * 32;
+            rt_tma_load_2d(xs_addr + (buf * RT_TILE_CHUNKS + b * 256) * 16, &map_x, bar, k0, (int)t0);
+            rt_tma_load_2d(cs_addr + (buf * RT_TILE_CHUNKS + b * 256) * 16, &map_c, bar, k0, e0);
+        }
+    };
+    if (tid == 0) {
+        for (int i = 0; i < RT_STAGES; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rt_smem_u32(&s_full[i])), "r"(1u) : "memory");
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first two stages of the first pass are fetched while the warps compute the row statistics
+        issue(0, 0, 0);
+        if (nstages > 1) issue(1, 1, 0);
+    }
+    if (use_ln) {
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const int ra = warp + 16 * p, rb = ra + 8;
+            float mean[2], rstd[2];
+            warp_two_row_stats<true>(X + (t0 + (t0 + ra < T ? ra : 0)) * (long long)D,
+                                     X + (t0 + (t0 + rb < T ? rb : 0)) * (long long)D, D, mean, rstd);
+            if (lane == 0) {
+                s_mean[ra] = mean[0];
+                s_rstd[ra] = rstd[0];
+                s_mean[rb] = mean[1];
+                s_rstd[rb] = rstd[1];
+            }
+        }
+    }
+    __syncthreads();
+
+    // compute role: partial index l = 8 (lane / 8) + warp, 16 tokens tt + 2 j, 8 experts te + 4 jj
+    const int l = 8 * (lane >> 3) + warp;
+    const int tt = (lane >> 2) & 1, te = lane & 3;
+    // normalising role: chunk (step, l) of rows rg + 4 r, r = 0..7
+    const int st_step = (tid >> 5) & 1, st_l = tid & 31, rg = tid >> 6;
+    const int st_k = st_step * 128 + st_l * 4;
+
+    auto load_gamma = [&](int stage) -> float4 {
+        const int k = stage * RT_STAGE_FLOATS + st_k;
+        return (use_ln && k < D) ? load_row4(gamma, k, D, true) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    // LayerNorm of the token chunks of this thread, in place; chunks past the row (zero-filled) stay zero
+    auto normalise = [&](int stage, uint32_t buf, const float4& g) {
+        const int k = stage * RT_STAGE_FLOATS + st_k;
+        if (k >= D) return;
+        float4* xt = xs + buf * RT_TILE_CHUNKS;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int row = rg + 4 * r;
+            if (t0 + row >= T) continue;
+            float4* xd = xt + rt_box_idx(st_step, st_l, row);
+            float4 v = *xd;
+            const float mean = s_mean[row], rstd = s_rstd[row];
+            v.x = ln_apply(v.x, mean, rstd, g.x);
+            v.y = ln_apply(v.y, mean, rstd, g.y);
+            v.z = ln_apply(v.z, mean, rstd, g.z);
+            v.w = ln_apply(v.w, mean, rstd, g.w);
+            *xd = v;
+        }
+    };
+
+    float best[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};   // reference plugin/cuda/moe.cu:26-27; tokens warp + 8 q
+    int best_e[4] = {-1, -1, -1, -1};
+    uint32_t gs = 0;
+    bool failed = false;
+
+    for (int e0 = 0; e0 < E && !failed; e0 += RT_EXPERTS) {
+        float acc[16][8];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) acc[j][jj] = 0.f;
+
+        if (tid == 0 && e0 > 0) {      // (the first pass's were issued before the statistics)
+            issue(gs, 0, e0);
+            if (nstages > 1) issue(gs + 1, 1, e0);
+        }
+        float4 g = load_gamma(0);
+        bool ok = rt_mbar_wait(rt_smem_u32(&s_full[gs % RT_STAGES]), (gs / RT_STAGES) & 1, abort_flag);
+        if (ok && use_ln) normalise(0, gs % RT_STAGES, g);
+        g = load_gamma(1);
+        if (__syncthreads_or(!ok)) { failed = true; break; }
+        for (int stage = 0; stage < nstages; ++stage) {
+            const uint32_t buf = (gs + stage) % RT_STAGES, next = (gs + stage + 1) % RT_STAGES;
+            // the buffer of stage + 2 was read in stage - 1, which every thread left before the last barrier
+            if (tid == 0 && stage + 2 < nstages) issue(gs + stage + 2, stage + 2, e0);
+            const float4* xt = xs + buf * RT_TILE_CHUNKS;
+            const float4* ct = cs + buf * RT_TILE_CHUNKS;
+#pragma unroll
+            for (int step = 0; step < RT_STEPS; ++step) {
+                if (stage * RT_STAGE_FLOATS + step * 128 >= D) break;
+                float4 c[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) c[jj] = ct[rt_box_idx(step, l, te + 4 * jj)];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float4 x = xt[rt_box_idx(step, l, tt + 2 * j)];
+                    // Elements past the end of a row are zero in both tiles: their products are exact zeros and
+                    // leave the partial sums' bits unchanged, so they need no predicate.
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.x, c[jj].x, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.y, c[jj].y, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.z, c[jj].z, acc[j][jj]);
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) acc[j][jj] = __fmaf_rn(x.w, c[jj].w, acc[j][jj]);
+                }
+            }
+            ok = true;
+            if (stage + 1 < nstages) {
+                const uint32_t gn = gs + stage + 1;
+                ok = rt_mbar_wait(rt_smem_u32(&s_full[next]), (gn / RT_STAGES) & 1, abort_flag);
+                if (ok && use_ln) normalise(stage + 1, next, g);
+                g = load_gamma(stage + 2);
+            }
+            // stage + 1 is complete for everybody; everybody is done with `stage`
+            if (__syncthreads_or(!ok)) { failed = true; break; }
+        }
+        if (failed) break;
+        gs += (uint32_t)nstages;
+
+        // the 32 partial sums of every (token, expert) pair, through shared memory
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+                red[l * RT_RED_L + (tt + 2 * j) * RT_RED_PITCH + te + 4 * jj] = acc[j][jj];
+        __syncthreads();
+        // the butterfly (xor 16, 8, 4, 2, 1 over l) and the argmax: warp -> tokens warp + 8 q, lane -> expert e0 + lane
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int t = warp + 8 * q;
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = red[i * RT_RED_L + t * RT_RED_PITCH + lane];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+                for (int i = 0; i < off; ++i) v[i] = __fadd_rn(v[i], v[i + off]);
+            // Candidates of this pass have higher indices than the running winner, so they replace it only when
+            // strictly greater; among themselves the lowest index wins a tie.  That is the expert the reference's
+            // sequential strict '>' scan keeps (plugin/cuda/moe.cu:62-67).  A NaN score is never greater.
+            float cand = v[0];
+            int cand_e = (e0 + lane < E && cand > best[q]) ? e0 + lane : -1;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                const float os = __shfl_xor_sync(0xffffffffu, cand, off);
+                const int oe = __shfl_xor_sync(0xffffffffu, cand_e, off);
+                if (oe >= 0 && (cand_e < 0 || os > cand || (os == cand && oe < cand_e))) {
+                    cand = os;
+                    cand_e = oe;
+                }
+            }
+            if (cand_e >= 0) {
+                best[q] = cand;
+                best_e[q] = cand_e;
+            }
+        }
+        __syncthreads();   // the partial sums have been read before the next pass refills the tiles
+    }
+    if (failed) {
+        // a copy never arrived: report it, give copies in flight time to land before the shared memory goes away
+        if (tid == 0 && status) atomicOr(status, STATUS_WAIT_TIMEOUT);
+        const unsigned long long w0 = rt_global_ns();
+        while (rt_global_ns() - w0 < 200000ull) __nanosleep(1000);
+        return;
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const long long t = t0 + warp + 8 * q;
             if (t >= T) continue;
             gate[t] = best_e[q];
             if (score) score[t] = best[q];
@@ -326,6 +608,39 @@ __global__ void select_top1_kernel(long long T, int E, const float* __restrict__
 
 }  // namespace
 
+namespace {
+// Tensor maps of the token rows and the centroids (boxes of 32 floats x 32 rows); the last few are kept per host
+// thread, because the same buffers come back call after call.
+int route_maps(CUtensorMap* mx, CUtensorMap* mc, const float* X, const float* C, long long T, int D, int E) {
+    struct Entry {
+        const float* base = nullptr;
+        long long rows = 0;
+        int D = 0;
+        CUtensorMap map;
+    };
+    static thread_local Entry cache[8];
+    static thread_local int next = 0;
+    auto get = [&](const float* base, long long rows, CUtensorMap* out) -> int {
+        for (const Entry& e : cache)
+            if (e.base == base && e.rows == rows && e.D == D) {
+                *out = e.map;
+                return INFMOE_OK;
+            }
+        Entry& e = cache[next];
+        next = (next + 1) % 8;
+        e.base = nullptr;
+        INFMOE_TRY(make_f32_row_map(&e.map, base, D, rows, 32));
+        e.base = base;
+        e.rows = rows;
+        e.D = D;
+        *out = e.map;
+        return INFMOE_OK;
+    };
+    INFMOE_TRY(get(X, T, mx));
+    return get(C, E, mc);
+}
+}  // namespace
+
 int launch_route(const float* X, const float* C, const float* gamma, long long T, int D, int E, int* gate,
                  float* score, int* status, cudaStream_t stream) {
     if (T < 0 || D <= 0 || E <= 0 || !X || !C || !gate) {
@@ -335,7 +650,13 @@ int launch_route(const float* X, const float* C, const float* gamma, long long T
     if (T == 0) return INFMOE_OK;
     const bool vec = (D % 4 == 0) && (((uintptr_t)X | (uintptr_t)C | (uintptr_t)gamma) % 16 == 0);
     const long long grid = (T + RT_TOKENS - 1) / RT_TOKENS;
-    if (vec) {
+    static const bool no_tma = [] { const char* v = getenv("INFMOE_ROUTE"); return v && !strcmp(v, "cp_async"); }();
+    CUtensorMap map_x, map_c;
+    if (vec && !no_tma && T < (1ll << 31) && route_maps(&map_x, &map_c, X, C, T, D, E) == INFMOE_OK) {
+        INFMOE_CUDA_TRY(cudaFuncSetAttribute(route_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM + 1024));
+        route_tma_kernel<<<(unsigned)grid, RT_THREADS, RT_SMEM + 1024, stream>>>(map_x, map_c, X, gamma, T, D, E, gate,
+                                                                               score, status);
+    } else if (vec) {
         INFMOE_CUDA_TRY(cudaFuncSetAttribute(route_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM));
         route_kernel<true><<<(unsigned)grid, RT_THREADS, RT_SMEM, stream>>>(X, C, gamma, T, D, E, gate, score, status);
     } else {
