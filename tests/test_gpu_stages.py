@@ -35,7 +35,9 @@ def test_route_known_answers(g, kat):
 
 @pytest.mark.parametrize("T,D,E,ln", [(1, 64, 4, False), (32, 64, 4, False), (33, 64, 4, True), (7, 10, 1, True),
                                       (300, 1000, 37, True), (129, 130, 17, False), (64, 4096, 32, True),
-                                      (40, 513, 130, True), (1000, 256, 64, False)])
+                                      (40, 513, 130, True), (1000, 256, 64, False),
+                                      # rows shorter than one 32-float box of the tiled copies, and just longer
+                                      (9, 4, 3, False), (50, 12, 5, True), (100, 36, 33, True), (31, 260, 65, True)])
 def test_route_bit_exact(g, oracle, T, D, E, ln):
     rng = np.random.default_rng(T * 131 + D)
     x = rng.standard_normal((T, D)).astype(np.float32)
