@@ -172,6 +172,42 @@ def test_split_operand_products_with_wide_value_ranges(oracle, case):
     assert err <= TOL, err
 
 
+def test_routing_and_dispatch_at_the_expert_parallel_size(oracle):
+    """65536 tokens, d_model 4096, 128 experts with the pre-gating LayerNorm (the expert-parallel configuration as
+    written): four expert passes per CTA.  Routing is per token, so a sample of the tokens is held against the
+    oracle bit for bit; dispatch is compared on all of them."""
+    import torch
+    from infmoe_b200 import capi
+    from tests import gpu_util as g
+    assert torch.cuda.is_available()
+    T, D, E = 65536, 4096, 128
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    dx = torch.randn(T, D, generator=gen, device="cuda")
+    dc = torch.randn(E, D, generator=gen, device="cuda") * 0.02
+    dl = 1 + 0.01 * torch.randn(D, generator=gen, device="cuda")
+    gate = torch.full((T,), -7, dtype=torch.int32, device="cuda")
+    score = torch.zeros(T, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    capi.check(capi.lib().infmoe_route(dx.data_ptr(), dc.data_ptr(), dl.data_ptr(), T, D, E, gate.data_ptr(),
+                                       score.data_ptr(), status.data_ptr(), g.stream()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    gate_h, score_h = gate.cpu().numpy(), score.cpu().numpy()
+    rng = np.random.default_rng(3)
+    rows = np.sort(np.concatenate([rng.choice(T, size=1500, replace=False), np.arange(T - 40, T), np.arange(40)]))
+    rows = np.unique(rows)
+    idx = torch.from_numpy(rows).cuda()
+    ogate, oscore = oracle.route(dx[idx].cpu().numpy(), dc.cpu().numpy(), dl.cpu().numpy())
+    np.testing.assert_array_equal(gate_h[rows], ogate)
+    np.testing.assert_array_equal(score_h[rows].view(np.uint32), oscore.view(np.uint32))
+    count, offset, pos, st = g.expert_count(gate_h, E)
+    oc, oo, op = oracle.dispatch(gate_h, E)
+    assert st == 0
+    np.testing.assert_array_equal(count, oc)
+    np.testing.assert_array_equal(offset, oo)
+    np.testing.assert_array_equal(pos, op)
+
+
 def test_identity_full_size_roundtrip():
     """Scatter then gather over 65536 x 4096 floats is the identity (the Identity sublayer)."""
     import torch
