@@ -41,9 +41,9 @@
 // truncation, not round-to-nearest: measured on B200, one accumulator carried
 // over K = 1024..2048 drifts by about 1.5e-5 relative, and the drift grows
 // linearly with the number of MMAs.  So a TMEM accumulator only ever holds the
-// sum of one chunk of 8 k blocks (64 MMAs, the first one overwriting); the
-// accumulate warps add each finished chunk into a running sum in registers
-// with round-to-nearest adds.
+// sum of one chunk of 8 k blocks (64 MMAs, the first one overwriting; the first
+// chunk of a tile is 12 or 16 blocks, see chunk_ends); the accumulate warps add
+// each finished chunk into a running sum in registers with round-to-nearest adds.
 //
 // Two MMA issuers, one accumulator each.  One thread can keep the tensor pipe full only while it does
 // nothing but issue; the barrier waits before a k block and the commits after it leave the pipe idle
@@ -251,7 +251,7 @@ constexpr int WBUFS = 3;                              // TMEM weight head/tail b
 constexpr int barrier_period(int n) { return n % 2 ? 2 * n : n; }
 constexpr int PW = barrier_period(WBUFS);
 constexpr int TMEM_COLS = 512;
-constexpr int CHUNK_BLOCKS = 8;                       // k blocks (of 12 MMAs) one accumulator takes between two drains
+constexpr int CHUNK_BLOCKS = 8;                       // k blocks (of 8 MMAs) one accumulator takes between two drains
 constexpr int W_TILE = UMMA_M * ROW_BYTES;            // 16 KB of raw FP32 weights per k block
 
 template <int NMAX, int W_STAGES, int T_STAGES>
