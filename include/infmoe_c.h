@@ -271,6 +271,14 @@ INFMOE_API int infmoe_ep_forward(infmoe_ep* ep, const float* d_x, float* d_out, 
 INFMOE_API int infmoe_ep_output(const infmoe_ep* ep, float** d_out);
 /* Host buffers in and out, copies inside; blocks until the result is there and returns the status. */
 INFMOE_API int infmoe_ep_forward_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_t tokens);
+/* The same without waiting (collective; every rank submits the same sequence): the step's upload, pass and
+ * download are enqueued and the call returns; infmoe_ep_wait_host blocks until the OLDEST submitted step's result is
+ * in its h_out and returns that step's status.  At most two steps may be in flight: the upload of one then runs
+ * behind the experts of the one before, its download under the one after.  h_x and h_out must be page-locked for
+ * the copies to overlap, and must stay untouched until the step has been waited for.  infmoe_ep_forward and
+ * infmoe_ep_forward_host refuse to run while steps are in flight. */
+INFMOE_API int infmoe_ep_submit_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_t tokens);
+INFMOE_API int infmoe_ep_wait_host(infmoe_ep* ep);
 /* Blocks until `stream` is idle; non-zero when this rank (or, for routing, any rank) raised a device-side status. */
 INFMOE_API int infmoe_ep_sync_status(infmoe_ep* ep, void* stream);
 /* Routing results of this rank's tokens in the last pass (as infmoe_layer_last_routing, expert indices global). */

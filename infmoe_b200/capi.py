@@ -145,6 +145,8 @@ SIGNATURES = {
     "infmoe_ep_forward_end": [_vp, _vp, _vp],
     "infmoe_ep_output": [_vp, ctypes.POINTER(_vp)],
     "infmoe_ep_forward_host": [_vp, _vp, _vp, _i64],
+    "infmoe_ep_submit_host": [_vp, _vp, _vp, _i64],
+    "infmoe_ep_wait_host": [_vp],
     "infmoe_ep_sync_status": [_vp, _vp],
     "infmoe_ep_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,
     "infmoe_ep_received": [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_i64)],

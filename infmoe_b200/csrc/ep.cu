@@ -80,7 +80,7 @@ SymLayout sym_layout(int world, long long cap, int D) {
     l.home = take(slots * 4);
     l.score = take(slots * 4);
     l.count = take((size_t)EP_MAX_WORLD * 4);
-    l.out = take((size_t)cap * (size_t)D * 4);
+    l.out = take(2 * (size_t)cap * (size_t)D * 4);   // two output buffers: see infmoe_ep_submit_host
     l.total = o;
     return l;
 }
@@ -122,12 +122,13 @@ ep_send_kernel(long long T, int D, int vec, const float* __restrict__ X, const i
 
 // Where the result of every filled slot goes: row home[slot] of the output buffer of the rank owning region slot / cap.
 __global__ void ep_prepare_kernel(long long slots, long long cap, int D, const int* __restrict__ count,
-                                  const int* __restrict__ home, EpPeers peers, unsigned long long* __restrict__ dst) {
+                                  const int* __restrict__ home, EpPeers peers, long long out_off,
+                                  unsigned long long* __restrict__ dst) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x; s < slots; s += stride) {
         const int src = (int)(s / cap);
         if ((int)(s - (long long)src * cap) < count[src])
-            dst[s] = (unsigned long long)(peers.out[src] + (long long)home[s] * D);
+            dst[s] = (unsigned long long)(peers.out[src] + out_off + (long long)home[s] * D);
     }
 }
 
@@ -221,6 +222,15 @@ struct infmoe_ep {
     float* d_x = nullptr;                // input staging of forward_host
     cudaStream_t own_stream = nullptr;
     long long tokens = 0;                // of the pass in flight
+    int out_sel = 0;                     // which of the two output buffers the pass in flight fills (same on all ranks)
+    // pipelined host path (infmoe_ep_submit_host / _wait_host): two steps in flight
+    float* d_xp[2] = {nullptr, nullptr};
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_sent[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr},
+                ev_out[2] = {nullptr, nullptr};
+    bool sent_once[2] = {false, false}, out_once[2] = {false, false};
+    int* h_step = nullptr;               // pinned [2][4]: status words of the two steps
+    long long submitted = 0, waited = 0;
 #if INFMOE_HAVE_NCCL
     ncclComm_t comm = nullptr;
 #endif
@@ -230,6 +240,8 @@ struct infmoe_ep {
 };
 
 namespace {
+
+long long ep_out_off(const infmoe_ep* ep) { return (long long)ep->out_sel * ep->cap * ep->D; }
 
 int ep_mark(infmoe_ep* ep, int mark, cudaStream_t stream) {
     if (!ep->profiling) return INFMOE_OK;
@@ -335,6 +347,14 @@ void ep_free(infmoe_ep* ep) {
                     ep->d_offset, ep->d_slot_dst, ep->d_status, ep->d_sync, ep->d_ws, ep->d_x};
     for (void* p : bufs)
         if (p) cudaFree(p);
+    for (int i = 0; i < 2; ++i) {
+        if (ep->d_xp[i]) cudaFree(ep->d_xp[i]);
+        for (cudaEvent_t e : {ep->ev_in[i], ep->ev_sent[i], ep->ev_done[i], ep->ev_out[i]})
+            if (e) cudaEventDestroy(e);
+    }
+    if (ep->h_step) cudaFreeHost(ep->h_step);
+    if (ep->in_stream) cudaStreamDestroy(ep->in_stream);
+    if (ep->out_stream) cudaStreamDestroy(ep->out_stream);
     if (ep->h_words) cudaFreeHost(ep->h_words);
     if (ep->own_stream) cudaStreamDestroy(ep->own_stream);
     for (auto e : ep->prof) cudaEventDestroy(e);
@@ -381,7 +401,7 @@ int ep_experts(infmoe_ep* ep, cudaStream_t stream) {
     const long long slots = (long long)ep->world * ep->cap;
     const unsigned grid = (unsigned)((slots + 255) / 256 < 1024 ? (slots + 255) / 256 : 1024);
     ep_prepare_kernel<<<grid, 256, 0, stream>>>(slots, ep->cap, ep->D, ep->peers.count[ep->rank], ep->peers.home[ep->rank],
-                                                ep->peers, ep->d_slot_dst);
+                                                ep->peers, ep_out_off(ep), ep->d_slot_dst);
     note_launch();
     INFMOE_CUDA_TRY(cudaGetLastError());
     INFMOE_TRY(layer_run_slots(ep->local, ep->peers.rows[ep->rank], ep->peers.expert[ep->rank],
@@ -392,13 +412,29 @@ int ep_experts(infmoe_ep* ep, cudaStream_t stream) {
 }
 
 int ep_end(infmoe_ep* ep, float* d_out, cudaStream_t stream) {
-    float* mine = ep->peers.out[ep->rank];
+    float* mine = ep->peers.out[ep->rank] + ep_out_off(ep);
     if (d_out && d_out != mine && ep->tokens > 0)
         INFMOE_CUDA_TRY(cudaMemcpyAsync(d_out, mine, sizeof(float) * (size_t)ep->tokens * ep->D, cudaMemcpyDeviceToDevice,
                                         stream));
     INFMOE_TRY(ep_mark(ep, 5, stream));
     if (ep->profiling) ep->prof_calls++;
     return INFMOE_OK;
+}
+
+// One whole pass on `stream`; after_send (or NULL) is recorded once the rows have left (the input is free again).
+int ep_pass(infmoe_ep* ep, const float* d_x, float* d_out, int64_t tokens, cudaStream_t stream, cudaEvent_t after_send) {
+    INFMOE_TRY(ep_begin(ep, d_x, tokens, stream));
+    if (after_send) INFMOE_CUDA_TRY(cudaEventRecord(after_send, stream));
+    // the status of routing and dispatch travels with the first barrier
+    ep_status_kernel<<<1, 1, 0, stream>>>(ep->d_status, nullptr, ep->d_sync);
+    note_launch();
+    INFMOE_CUDA_TRY(cudaGetLastError());
+    INFMOE_TRY(ep_barrier(ep, stream));       // every rank's rows have arrived
+    INFMOE_TRY(ep_mark(ep, 2, stream));
+    INFMOE_TRY(ep_experts(ep, stream));
+    INFMOE_TRY(ep_barrier(ep, stream));       // every rank's results have been stored
+    INFMOE_TRY(ep_mark(ep, 4, stream));
+    return ep_end(ep, d_out, stream);
 }
 
 }  // namespace
@@ -608,18 +644,12 @@ int infmoe_ep_forward(infmoe_ep* ep, const float* d_x, float* d_out, int64_t tok
         set_error("ep_forward: loopback ranks are driven phase by phase (forward_begin / _experts / _end)");
         return INFMOE_ERR_STATE;
     }
-    cudaStream_t stream = (cudaStream_t)stream_v;
-    INFMOE_TRY(ep_begin(ep, d_x, tokens, stream));
-    // the status of routing and dispatch travels with the first barrier
-    ep_status_kernel<<<1, 1, 0, stream>>>(ep->d_status, nullptr, ep->d_sync);
-    note_launch();
-    INFMOE_CUDA_TRY(cudaGetLastError());
-    INFMOE_TRY(ep_barrier(ep, stream));       // every rank's rows have arrived
-    INFMOE_TRY(ep_mark(ep, 2, stream));
-    INFMOE_TRY(ep_experts(ep, stream));
-    INFMOE_TRY(ep_barrier(ep, stream));       // every rank's results have been stored
-    INFMOE_TRY(ep_mark(ep, 4, stream));
-    return ep_end(ep, d_out, stream);
+    if (ep->submitted != ep->waited) {
+        set_error("ep_forward: steps submitted with infmoe_ep_submit_host are still in flight");
+        return INFMOE_ERR_STATE;
+    }
+    ep->out_sel = 0;
+    return ep_pass(ep, d_x, d_out, tokens, (cudaStream_t)stream_v, nullptr);
 }
 
 int infmoe_ep_output(const infmoe_ep* ep, float** d_out) {
@@ -627,7 +657,7 @@ int infmoe_ep_output(const infmoe_ep* ep, float** d_out) {
         set_error("ep_output: null argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
-    *d_out = ep->peers.out[ep->rank];
+    *d_out = ep->peers.out[ep->rank] + (long long)ep->out_sel * ep->cap * ep->D;
     return INFMOE_OK;
 }
 
@@ -662,6 +692,10 @@ int infmoe_ep_forward_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_
         set_error("ep_forward_host: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
+    if (ep->submitted != ep->waited) {
+        set_error("ep_forward_host: steps submitted with infmoe_ep_submit_host are still in flight");
+        return INFMOE_ERR_STATE;
+    }
     if (!ep->own_stream) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&ep->own_stream, cudaStreamNonBlocking));
     if (!ep->d_x) INFMOE_CUDA_TRY(cudaMalloc(&ep->d_x, sizeof(float) * (size_t)ep->cap * ep->D));
     const size_t io = sizeof(float) * (size_t)tokens * ep->D;
@@ -670,6 +704,95 @@ int infmoe_ep_forward_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_
     if (tokens > 0)
         INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, ep->peers.out[ep->rank], io, cudaMemcpyDeviceToHost, ep->own_stream));
     return infmoe_ep_sync_status(ep, ep->own_stream);
+}
+
+// Up to two steps in flight: the upload of a step runs on a copy stream behind the previous step's experts, its
+// download on another one under the next step's; two input stagings and the two output buffers of the symmetric
+// allocation make that safe.  Before a rank joins the first barrier of a step it has finished copying out the output
+// buffer the step is going to fill, so after that barrier every rank may store into it.
+int infmoe_ep_submit_host(infmoe_ep* ep, const float* h_x, float* h_out, int64_t tokens) {
+    if (!ep || tokens < 0 || tokens > (ep ? ep->cap : 0) || (tokens > 0 && (!h_x || !h_out))) {
+        set_error("ep_submit_host: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (ep->loopback && ep->world > 1) {
+        set_error("ep_submit_host: loopback ranks are driven phase by phase");
+        return INFMOE_ERR_STATE;
+    }
+    if (ep->submitted - ep->waited >= 2) {
+        set_error("ep_submit_host: two steps are in flight already; call infmoe_ep_wait_host first");
+        return INFMOE_ERR_STATE;
+    }
+    if (!ep->own_stream) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&ep->own_stream, cudaStreamNonBlocking));
+    if (!ep->in_stream) {
+        INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&ep->in_stream, cudaStreamNonBlocking));
+        INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&ep->out_stream, cudaStreamNonBlocking));
+        INFMOE_CUDA_TRY(cudaHostAlloc(&ep->h_step, 32, cudaHostAllocDefault));
+        memset(ep->h_step, 0, 32);
+        for (int i = 0; i < 2; ++i) {
+            INFMOE_CUDA_TRY(cudaMalloc(&ep->d_xp[i], sizeof(float) * (size_t)ep->cap * ep->D));
+            for (cudaEvent_t* e : {&ep->ev_in[i], &ep->ev_sent[i], &ep->ev_done[i], &ep->ev_out[i]})
+                INFMOE_CUDA_TRY(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        }
+    }
+    const int s = (int)(ep->submitted & 1);
+    const size_t io = sizeof(float) * (size_t)tokens * ep->D;
+    cudaStream_t main = ep->own_stream;
+    // upload: the staging buffer is free once the step that used it last has sent its rows
+    if (ep->sent_once[s]) INFMOE_CUDA_TRY(cudaStreamWaitEvent(ep->in_stream, ep->ev_sent[s], 0));
+    if (tokens > 0) INFMOE_CUDA_TRY(cudaMemcpyAsync(ep->d_xp[s], h_x, io, cudaMemcpyHostToDevice, ep->in_stream));
+    INFMOE_CUDA_TRY(cudaEventRecord(ep->ev_in[s], ep->in_stream));
+    INFMOE_CUDA_TRY(cudaStreamWaitEvent(main, ep->ev_in[s], 0));
+    // the output buffer this step fills has been copied out (by this rank; the barrier of the pass tells the others)
+    if (ep->out_once[s]) INFMOE_CUDA_TRY(cudaStreamWaitEvent(main, ep->ev_out[s], 0));
+    ep->out_sel = s;
+    INFMOE_TRY(ep_pass(ep, ep->d_xp[s], nullptr, tokens, main, ep->ev_sent[s]));
+    ep->sent_once[s] = true;
+    // the step's status words, for infmoe_ep_wait_host
+    int* hs = ep->h_step + 4 * s;
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(hs, ep->d_status, 4, cudaMemcpyDeviceToHost, main));
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(hs + 1, ep->d_sync, 4, cudaMemcpyDeviceToHost, main));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(ep->d_status, 0, 4, main));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(ep->d_sync, 0, 8, main));
+    INFMOE_TRY(layer_snapshot_status(ep->local, hs + 2, main));
+    INFMOE_CUDA_TRY(cudaEventRecord(ep->ev_done[s], main));
+    // download
+    INFMOE_CUDA_TRY(cudaStreamWaitEvent(ep->out_stream, ep->ev_done[s], 0));
+    if (tokens > 0)
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, ep->peers.out[ep->rank] + ep_out_off(ep), io, cudaMemcpyDeviceToHost,
+                                        ep->out_stream));
+    INFMOE_CUDA_TRY(cudaEventRecord(ep->ev_out[s], ep->out_stream));
+    ep->out_once[s] = true;
+    ep->submitted++;
+    return INFMOE_OK;
+}
+
+int infmoe_ep_wait_host(infmoe_ep* ep) {
+    if (!ep) {
+        set_error("ep_wait_host: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (ep->waited == ep->submitted) {
+        set_error("ep_wait_host: nothing in flight");
+        return INFMOE_ERR_STATE;
+    }
+    const int s = (int)(ep->waited & 1);
+    INFMOE_CUDA_TRY(cudaEventSynchronize(ep->ev_out[s]));
+    ep->waited++;
+    int* hs = ep->h_step + 4 * s;
+    const int mine = hs[0], anyone = hs[1], local = hs[2];
+    hs[0] = hs[1] = hs[2] = 0;
+    const int rc_local = layer_status_code(local);
+    if (rc_local != INFMOE_OK) return rc_local;
+    if (mine & (STATUS_NO_EXPERT | STATUS_BAD_GATE)) {
+        set_error("routing selected no expert for at least one token of this rank (NaN in input or centroids)");
+        return INFMOE_ERR_NAN;
+    }
+    if (anyone) {
+        set_error("another rank reported device status 0x%x during routing", anyone);
+        return INFMOE_ERR_NAN;
+    }
+    return INFMOE_OK;
 }
 
 int infmoe_ep_last_routing(const infmoe_ep* ep, const int32_t** gate, const float** score, const int32_t** pos,

@@ -1235,6 +1235,26 @@ int layer_run_slots(infmoe_layer* L, const float* d_rows, const int32_t* d_exper
 }
 }  // namespace infmoe
 
+namespace infmoe {
+
+int layer_snapshot_status(infmoe_layer* L, int* h_word, cudaStream_t stream) {
+    if (!L || !h_word) {
+        set_error("layer_snapshot_status: null argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (!L->device_ready) {
+        *h_word = 0;
+        return INFMOE_OK;
+    }
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(h_word, L->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    INFMOE_CUDA_TRY(cudaMemsetAsync(L->d_status, 0, sizeof(int), stream));
+    return INFMOE_OK;
+}
+
+int layer_status_code(int word) { return status_to_rc(word); }
+
+}  // namespace infmoe
+
 extern "C" {
 
 int infmoe_layer_sync_status(infmoe_layer* L, void* stream_v) {

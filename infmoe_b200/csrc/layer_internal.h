@@ -20,4 +20,9 @@ int layer_run_slots(infmoe_layer* layer, const float* d_rows, const int32_t* d_e
                     size_t workspace_bytes, int64_t slots, const int32_t* d_region_count, int32_t region_size,
                     cudaStream_t stream);
 
+// Copies the layer's device status word into *h_word (page-locked) and clears it, stream ordered, without waiting;
+// layer_status_code turns such a word into the return code infmoe_layer_sync_status would give.
+int layer_snapshot_status(infmoe_layer* layer, int* h_word, cudaStream_t stream);
+int layer_status_code(int word);
+
 }  // namespace infmoe

@@ -102,6 +102,14 @@ class NativeExpertParallel:
     def forward_host_ptr(self, h_in: int, h_out: int, tokens: int) -> None:
         capi.check(capi.lib().infmoe_ep_forward_host(self._h, h_in, h_out, int(tokens)))
 
+    def submit_host_ptr(self, h_in: int, h_out: int, tokens: int) -> None:
+        """Enqueues a step with host buffers and returns; at most two steps in flight (see wait_host)."""
+        capi.check(capi.lib().infmoe_ep_submit_host(self._h, h_in, h_out, int(tokens)))
+
+    def wait_host(self) -> None:
+        """Blocks until the oldest submitted step's result is in its output buffer; raises on its status."""
+        capi.check(capi.lib().infmoe_ep_wait_host(self._h))
+
     def sync_status(self, stream: Optional[int] = None) -> None:
         import torch
 

@@ -123,6 +123,33 @@ def test_loopback_reports_nan_rows_and_serves_the_others(oracle):
         l.terminate()
 
 
+def _pipelined_steps(ep, hx, want, tokens, steps=5):
+    """Steps submitted with two in flight: step k brings the rows rolled by k; every token must get the bits of the
+    synchronous call, whatever runs beside it on the copy streams."""
+    import torch
+    from infmoe_b200 import capi
+    ins = [torch.roll(hx, k, 0).contiguous().pin_memory() for k in range(steps)]
+    outs = [torch.full_like(hx, float("nan")).pin_memory() for _ in range(steps)]
+    for k in range(steps):
+        ep.submit_host_ptr(ins[k].data_ptr(), outs[k].data_ptr(), tokens)
+        if k >= 1:
+            ep.wait_host()
+    # one step is still in flight: a synchronous call is refused, a second submission is fine, a third is refused
+    extra = torch.full_like(hx, float("nan")).pin_memory()
+    with pytest.raises(capi.InfMoEError):
+        ep.forward_host_ptr(ins[0].data_ptr(), extra.data_ptr(), tokens)
+    ep.submit_host_ptr(ins[0].data_ptr(), extra.data_ptr(), tokens)
+    with pytest.raises(capi.InfMoEError):
+        ep.submit_host_ptr(ins[0].data_ptr(), extra.data_ptr(), tokens)
+    ep.wait_host()
+    ep.wait_host()
+    with pytest.raises(capi.InfMoEError):        # nothing left to wait for
+        ep.wait_host()
+    assert torch.equal(extra, want)
+    for k in range(steps):
+        assert torch.equal(outs[k], torch.roll(want, k, 0)), k
+
+
 def test_world_of_one_is_the_single_gpu_layer(oracle):
     import torch
     assert torch.cuda.is_available()
@@ -139,6 +166,9 @@ def test_world_of_one_is_the_single_gpu_layer(oracle):
     single = MoELayer.create(w.expert_count, w.embedding_size, w.hidden_size, 2, c, None, "T5_FF", "base_layer", ln)
     for e, ex in enumerate(experts):
         single.set_expert(e, *ex)
+    np.testing.assert_array_equal(hout.numpy(), single.forward_host(x))
+    _pipelined_steps(ep, hx, hout.clone(), w.tokens)
+    ep.forward_host_ptr(hx.data_ptr(), hout.data_ptr(), w.tokens)       # the synchronous call works again afterwards
     np.testing.assert_array_equal(hout.numpy(), single.forward_host(x))
     ep.destroy()
     local.terminate()
@@ -178,6 +208,7 @@ def _worker(rank, world, port, variant, ret):
         hout = torch.empty_like(hx).pin_memory()
         ep.forward_host_ptr(hx.data_ptr(), hout.data_ptr(), per)
         assert torch.equal(hout, out.cpu())
+        _pipelined_steps(ep, hx, out.cpu(), per)
         ret[rank] = dict(out=out.cpu().numpy(), gate=read_device(ep.last_routing()[0], per, np.int32))
         dist.barrier()
         ep.destroy()
