@@ -151,6 +151,27 @@ def _measure(total, scaling, steps, warmup, torch, dist, dev, rank, world, peaks
         sync_all()
         e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        # the same steps with two in flight (infmoe_ep_submit_host): a step's upload runs behind the experts of the
+        # step before, its download under the step after
+        hx2, hout2 = hx.clone().pin_memory(), torch.empty_like(hx).pin_memory()
+        bufs = [(hx, hout), (hx2, hout2)]
+        for i in range(2):          # warm-up: the first submission creates the copy streams and staging buffers
+            ep.submit_host_ptr(bufs[i][0].data_ptr(), bufs[i][1].data_ptr(), T_local)
+        ep.wait_host()
+        ep.wait_host()
+        hout.zero_()
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            a, b = bufs[i & 1]
+            ep.submit_host_ptr(a.data_ptr(), b.data_ptr(), T_local)
+            if i >= 1:
+                ep.wait_host()
+        ep.wait_host()
+        sync_all()
+        pipe_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / steps], device=dev)
+        dist.all_reduce(pipe_ms, op=dist.ReduceOp.MAX)
+        pipe_same = bool(torch.equal(hout, out_dev.cpu())) and (steps < 2 or bool(torch.equal(hout2, out_dev.cpu())))
         # host <-> device copy rates with every rank copying at once (they share the host's memory and PCIe roots)
         rates = []
         for src, dst in ((hx, dx), (out_dev, hout)):
@@ -164,7 +185,8 @@ def _measure(total, scaling, steps, warmup, torch, dist, dev, rank, world, peaks
         dist.all_reduce(rates_t, op=dist.ReduceOp.MIN)
         e2e = {"ms": float(e2e_ms.item()), "h2d_gbs_per_rank_min": float(rates_t[0].item()),
                "d2h_gbs_per_rank_min": float(rates_t[1].item()),
-               "same_bits_as_device_path": bool(torch.equal(hout, out_dev.cpu()))}
+               "same_bits_as_device_path": bool(torch.equal(hout, out_dev.cpu())),
+               "two_in_flight_ms": float(pipe_ms.item()), "two_in_flight_same_bits": pipe_same}
     clocks.__exit__()
 
     cnt_p, _, _, _ = ep.received()
@@ -230,7 +252,8 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
                              "tokens": c4.tokens, "value": c4.tokens / (r["ms"] * 1e-3), "unit": unit,
                              "ms_per_step": r["ms"], "phase_ms_rank0": r["phase_ms_rank0"],
                              "stage_ms_rank0": r["stage_ms_rank0"], "parity": r["parity"],
-                             "e2e": {"value": c4.tokens / (r["e2e"]["ms"] * 1e-3), "ms_per_step": r["e2e"]["ms"]}
+                             "e2e": {"value": c4.tokens / (r["e2e"]["ms"] * 1e-3), "ms_per_step": r["e2e"]["ms"],
+                                     "two_in_flight_ms_per_step": r["e2e"]["two_in_flight_ms"]}
                              if r["e2e"] else None}
             except Exception as exc:  # the headline line must not depend on the extra case
                 extra = {"workload": "ep_cpm2", "error": f"{type(exc).__name__}: {exc}"}
@@ -253,7 +276,10 @@ def run(args, total, scaling, metric, unit, clock_sampler_cls, peaks_fn, workloa
                     "h2d_bytes_per_step": main["hx_bytes"] * world, "d2h_bytes_per_step": main["hx_bytes"] * world,
                     "ms_per_step": e2e["ms"], "h2d_gbs_per_rank_min": e2e["h2d_gbs_per_rank_min"],
                     "d2h_gbs_per_rank_min": e2e["d2h_gbs_per_rank_min"],
-                    "same_bits_as_device_path": e2e["same_bits_as_device_path"], "host_placement_rank0": numa},
+                    "same_bits_as_device_path": e2e["same_bits_as_device_path"], "host_placement_rank0": numa,
+                    "two_in_flight": {"value": T_total / (e2e["two_in_flight_ms"] * 1e-3), "unit": unit,
+                                      "ms_per_step": e2e["two_in_flight_ms"],
+                                      "same_output": e2e["two_in_flight_same_bits"]}},
             "gpu_launches": main["launches"], "stage_ms_rank0": main["stage_ms_rank0"],
             "phase_ms_rank0": main["phase_ms_rank0"], "rows_received_rank0": main["rows_received_rank0"],
             "per_rank": main["per_rank"], "parity": main["parity"], "roofline": main["roofline"], "cpu_baseline": None, "clocks": main["clocks"],
