@@ -56,18 +56,23 @@
 // of the two accumulators are half a chunk apart, so while one accumulator is read out the other
 // issuer keeps the pipe busy; the same overlap hides the epilogue behind the next tile's MMAs.
 //
-// Pipeline per CTA (persistent, one CTA per SM, 16 warps):
+// Pipeline per CTA (persistent, one CTA per SM, 16 warps in four warpgroups, so that setmaxnreg can move
+// registers from the single-thread roles to the warps that hold the running sums: 56 / 168 / 120 per thread):
 //   warp 0        TMA producer of the weight ring (W_STAGES x 16 KB, raw FP32)
-//   warp 1, 15    MMA issuers for even / odd k blocks into accumulator 0 / 1 (warp 1 also owns the TMEM
+//   warp 1, 3     MMA issuers for even / odd k blocks into accumulator 0 / 1 (warp 1 also owns the TMEM
 //                 allocation); a commit per k block frees the token stage and the TMEM weight buffer,
 //                 a commit per chunk hands the issuer's accumulator to the accumulate warps
-//   warps 2..9    accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and every other
+//   warp 2        TMA producer of the token ring (T_STAGES x two planes)
+//   warps 4..11   accumulate + epilogue: tcgen05.ld the chunk (one TMEM lane quarter and every other
 //                 16-column slice per warp), add into registers; after the last chunk gelu*dot and its
 //                 split (lane pairs exchange a and b by shuffle) or residual add, stores contiguous
 //                 over the weight-row index
-//   warps 10..13  transform: weight tile shared memory -> registers -> head / packed BF16 -> TMEM
-//   warp 14       TMA producer of the token ring (T_STAGES x two planes)
-// TMEM columns: accumulators at 0 and 160, weight buffers (32 head + 32 packed columns) at 320, 384, 448.
+//   warps 12..15  transform: weight tile shared memory -> registers -> head / packed BF16 -> TMEM
+// TMEM columns: accumulators at 0 and 192 (a token chunk has up to 192 tokens), two weight buffers (32 head + 32
+// packed columns) at 384 and 448.  Two buffers feed the MMAs as well as three did; the 64 columns went to the
+// accumulators, because an expert with more tokens than a chunk holds costs a second pass over its weights, and
+// with 128 tokens per expert on average a limit of 160 is exceeded by one expert in a few hundred, which is enough
+// to give one rank in four of an expert-parallel run an extra round of tiles.
 // Tiles are (expert, 128-row weight block, token chunk); the list is derived in
 // the kernel from offset[E+1], so no host synchronisation is needed.  Every
 // mbarrier wait is bounded: on expiry the CTA raises STATUS_WAIT_TIMEOUT, lets
@@ -131,7 +136,7 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parit
 // Bounded wait.  Returns false when the wait was abandoned (limit reached here or in another role).
 // The slow path is a real function call (about 200 cycles on B200); the common case, a barrier
 // that is already complete, is a single inlined try_wait (about 17 cycles).
-__device__ __noinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+static __device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                unsigned long long limit_ns) {
     const unsigned long long t0 = global_ns();
     while (true) {
@@ -212,6 +217,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// Register redistribution between warpgroups (four consecutive warps): every warp of the group executes it.
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 constexpr int BK = 32;                     // k block: 32 floats = one 128-byte swizzled row
@@ -236,15 +246,24 @@ __device__ __forceinline__ uint32_t make_idesc(int n, uint32_t fmt) {
 
 enum { EPI_GELU_PAIR = 0, EPI_RESIDUAL = 1 };
 
+// Roles by warpgroup (four consecutive warps), so that registers can be moved between them (setmaxnreg): the four
+// single-thread roles give most of theirs to the accumulate warps, which hold the running sums of up to 12 slices.
+constexpr int W_WARP = 0;                             // TMA producer of the weight ring
+constexpr int MMA1_WARP = 1;                          // MMA issuer of the even k blocks; owns the TMEM allocation
+constexpr int TOKEN_WARP = 2;                         // TMA producer of the token ring
+constexpr int MMA2_WARP = 3;                          // MMA issuer of the odd k blocks
+constexpr int EPI_WARP0 = 4;
 constexpr int EPI_WARPS = 8;                          // two warps per TMEM lane quarter
+constexpr int XF_WARP0 = EPI_WARP0 + EPI_WARPS;
 constexpr int XF_WARPS = 4;                           // one transform warp per TMEM lane quarter
-constexpr int TOKEN_WARP = 2 + EPI_WARPS + XF_WARPS;  // TMA producer of the token ring
-constexpr int MMA2_WARP = TOKEN_WARP + 1;             // second MMA issuer (odd k blocks)
-constexpr int GEMM_THREADS = (MMA2_WARP + 1) * 32;
-constexpr int ACC_STRIDE = 160;                       // TMEM columns between the two accumulators
+constexpr int GEMM_THREADS = (XF_WARP0 + XF_WARPS) * 32;
+constexpr int REGS_SINGLE_ROLES = 56, REGS_EPILOGUE = 168, REGS_TRANSFORM = 120;   // per thread, after setmaxnreg
+static_assert(4 * 32 * REGS_SINGLE_ROLES + EPI_WARPS * 32 * REGS_EPILOGUE + XF_WARPS * 32 * REGS_TRANSFORM <=
+                  GEMM_THREADS * 128, "the roles share the registers the CTA was launched with (128 per thread)");
+constexpr int ACC_STRIDE = 192;                       // TMEM columns between the two accumulators
 constexpr int WBUF_COL = 2 * ACC_STRIDE;              // first TMEM column of the weight head/tail buffers
 constexpr int WBUF_STRIDE = 2 * BK;                   // head (BK columns) then tail (BK columns)
-constexpr int WBUFS = 3;                              // TMEM weight head/tail buffers
+constexpr int WBUFS = 2;                              // TMEM weight head/tail buffers
 // A ring of n buffers whose consecutive uses alternate between the two MMA issuers needs one barrier per
 // (buffer, issuer) pair, so that each issuer observes every phase of the barriers it waits on: a waiter
 // that skips phases of a shared barrier can take a stale completion for its own.
@@ -297,7 +316,7 @@ __device__ __forceinline__ bool chunk_ends(int kb, int KB) {
 
 // Tensor maps of the two token planes, one per box height 16, 32, ... 160 rows: a tile's load fetches exactly
 // the rows its MMAs read (n_pad), not the largest tile's worth.
-constexpr int TOKEN_BOXES = 10;
+constexpr int TOKEN_BOXES = 12;
 struct TokenMaps {
     CUtensorMap hi[TOKEN_BOXES], pk[TOKEN_BOXES];
 };
@@ -429,7 +448,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == MMA1_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
                      "r"((uint32_t)TMEM_COLS)
                      : "memory");
@@ -442,7 +461,9 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int total_tiles = s_prefix[args.E];
     volatile int* abort_flag = &s_abort;
 
-    if (warp == 0) {
+    if (warp < EPI_WARP0) {
+    setmaxnreg_dec<REGS_SINGLE_ROLES>();   // warps 0..3: one thread each does the work; the registers go to the others
+    if (warp == W_WARP) {
         // ================= TMA producer, weights =================
         // Runs up to W_STAGES k blocks ahead of the transform warps, independently of the token ring.
         if (lane == 0) {
@@ -488,12 +509,12 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (!ok) break;
             }
         }
-    } else if (warp == 1 || warp == MMA2_WARP) {
+    } else if (warp == MMA1_WARP || warp == MMA2_WARP) {
         // ================= MMA issuers =================
         // Warp 1 issues the even k blocks (counted over all tiles of the CTA) into accumulator 0, the
         // other warp the odd ones into accumulator 1.  The whole warp runs the loop so that addresses
         // and descriptors stay warp-uniform; one lane issues the tcgen05 instructions.
-        const uint32_t mine = warp == 1 ? 0u : 1u;
+        const uint32_t mine = warp == MMA1_WARP ? 0u : 1u;
         const bool leader = lane == 0;
         const uint32_t d = tmem_base + mine * ACC_STRIDE;
         const uint32_t acc_empty = smem_u32(&s_acc_empty[mine]), acc_full = smem_u32(&s_acc_full[mine]);
@@ -541,14 +562,16 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
             if (!ok) break;
         }
-    } else if (warp < 2 + EPI_WARPS) {
-        // ================= accumulate + epilogue (warps 2..9) =================
+    }
+    } else if (warp < XF_WARP0) {
+        setmaxnreg_inc<REGS_EPILOGUE>();   // takes what the other warpgroups gave back
+        // ================= accumulate + epilogue (warps 4..11) =================
         // Each chunk is accumulated in TMEM (its first MMA overwrites the accumulator) and added
         // here, with round-to-nearest adds, to a running sum in registers; then the accumulator
         // goes back to its MMA issuer.  The chunks of the two accumulators are taken in the fixed
         // order of their last k block.
         const int q = warp & 3;                 // TMEM lane quarter this warp may access
-        const int half = (warp - 2) >> 2;       // even or odd 16-column slices
+        const int half = (warp - EPI_WARP0) >> 2;   // even or odd 16-column slices
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
         // first hand-over: both accumulators are free
         mbar_arrive(smem_u32(&s_acc_empty[0]));
@@ -665,7 +688,8 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
         }
     } else {
-        // ================= transform (warps 10..13) =================
+        // ================= transform =================
+        setmaxnreg_dec<REGS_TRANSFORM>();
         // Thread = one weight row of the tile.  The row's 128 bytes are read from the swizzled
         // shared-memory tile (16-byte chunk c of row r sits at chunk c ^ (r & 7)), split into
         // TF32 head and tail, and stored into this thread's TMEM lane.
@@ -747,7 +771,7 @@ ffn_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 1) {
+    if (warp == MMA1_WARP) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                      : "memory");
@@ -938,9 +962,9 @@ int launch_ffn_umma(long long T, int D, int F, int E, int e_begin, int e_end, co
         INFMOE_TRY((launch_one<EPI_RESIDUAL, NMAX, WS, TS>(a2, T, slots, wo, g_hi, g_lo, num_sms, stream)));      \
     } while (0)
     switch (variant) {
-        case 1: INFMOE_LAUNCH_PAIR(160, 3, 4); break;
+        case 1: INFMOE_LAUNCH_PAIR(160, 5, 3); break;
         case 2: INFMOE_LAUNCH_PAIR(144, 4, 4); break;
-        default: INFMOE_LAUNCH_PAIR(160, 5, 3); break;
+        default: INFMOE_LAUNCH_PAIR(192, 4, 3); break;
     }
 #undef INFMOE_LAUNCH_PAIR
     return INFMOE_OK;
