@@ -41,7 +41,7 @@ from infmoe_b200 import synth  # noqa: E402
 # capture of workload cpm2_profile (profiles/ffn_umma_kernel_cpm2_profile.md) divided by the weight elements that
 # launch streams; 4 = each raw FP32 weight crosses HBM once.  It is a figure from that capture, scaled by the
 # elements this launch streams -- it is not measured by this run.
-TRAFFIC_BYTES_PER_WEIGHT = 4.29
+TRAFFIC_BYTES_PER_WEIGHT = 4.27
 TRAFFIC_SOURCE = "ncu capture of cpm2_profile (profiles/ffn_umma_kernel_cpm2_profile.md), bytes per weight element x elements streamed"
 
 METRIC = "moe_layer_tokens_per_s"
