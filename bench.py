@@ -8,14 +8,21 @@ With N = 1 the workload is the CPM-2-style layer the headline metric is quoted o
 (E=32, d_model=4096, d_ff=10240, 8x512 tokens, all experts resident).  With N > 1
 (launched under torch.distributed.run, one rank per GPU) the experts are sharded
 expert-parallel, every rank keeps the same number of local tokens and local
-experts (weak scaling), and tokens move with an NCCL all-to-all.
+experts (weak scaling), and rows and results move by peer stores over NVLink
+(infmoe_ep_forward; NCCL only as the barrier).
 
 One JSON line is printed by rank 0.  `value` is whole-job tokens/s with the input
 already in HBM, timed on the device with CUDA events (max over ranks); `e2e` is
 the same metric through the host-buffer entry point of the C ABI with the
-host<->device copies inside the timed region.  `roofline` describes the dominant
-kernel (the gated wi_0/wi_1 grouped GEMM); `cpu_baseline` is the CPU restatement
-of the reference's math timed on this box's host cores on a bounded sample.
+host<->device copies inside the timed region, one blocking call per step; beside
+it `e2e.two_contexts` (N = 1: two clones driven by two host threads) and
+`e2e.two_in_flight` (N > 1: infmoe_ep_submit_host / _wait_host) give the rate
+when a step's copies may overlap its neighbours' passes.  `roofline` describes
+the dominant kernel (the gated wi_0/wi_1 grouped GEMM): `frac` against the
+ceiling of the MMAs it issues, `frac_3xtf32` against plain 3xTF32; `cpu_baseline`
+is the CPU restatement of the reference's math timed on this box's host cores on
+a bounded sample.  N > 1 adds `per_rank` (expert time, wait time, received rows
+and SM clock of every rank) and the fixed-size 128-expert case under `ep_cpm2`.
 
 --impl reference times that CPU restatement alone (the reference itself has no CPU
 path and its TensorRT plugin cannot be built here), on all host threads.
