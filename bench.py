@@ -15,9 +15,10 @@ One JSON line is printed by rank 0.  `value` is whole-job tokens/s with the inpu
 already in HBM, timed on the device with CUDA events (max over ranks); `e2e` is
 the same metric through the host-buffer entry point of the C ABI with the
 host<->device copies inside the timed region, one blocking call per step; beside
-it `e2e.two_contexts` (N = 1: two clones driven by two host threads) and
-`e2e.two_in_flight` (N > 1: infmoe_ep_submit_host / _wait_host) give the rate
-when a step's copies may overlap its neighbours' passes.  `roofline` describes
+it `e2e.two_in_flight` (infmoe_layer_submit_host / infmoe_ep_submit_host and
+the matching _wait_host: two steps in flight from one context) and, at N = 1,
+`e2e.two_contexts` (two clones driven by two host threads) give the rate when a
+step's copies may overlap its neighbours' passes.  `roofline` describes
 the dominant kernel (the gated wi_0/wi_1 grouped GEMM): `frac` against the
 ceiling of the MMAs it issues, `frac_3xtf32` against plain 3xTF32; `cpu_baseline`
 is the CPU restatement of the reference's math timed on this box's host cores on
@@ -346,6 +347,29 @@ def run_single(args, w):
     # ---- the same call from two execution contexts: a clone each, with its own stream and host buffers, driven by
     # ---- its own host thread (TensorRT gives every execution context a clone of the plugin).  The upload of one
     # ---- context's input runs behind the other's GEMMs.  Reported beside the one-context figure, not instead of it.
+    # ---- the same steps with two in flight from ONE context (infmoe_layer_submit_host / _wait_host): a step's
+    # ---- upload runs on a copy stream behind the pass of the step before
+    two_in_flight = None
+    if not w.streamed:
+        hx_b, hout_b = hx.clone().pin_memory(), torch.empty_like(hx).pin_memory()
+        bufs = [(hx, hout), (hx_b, hout_b)]
+        for i in range(2):                      # warm-up: the first submission creates streams and staging buffers
+            layer.submit_host_ptr(bufs[i][0].data_ptr(), bufs[i][1].data_ptr(), T)
+        layer.wait_host()
+        layer.wait_host()
+        keep = hout.clone()
+        hout.zero_()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            a, b = bufs[i & 1]
+            layer.submit_host_ptr(a.data_ptr(), b.data_ptr(), T)
+            if i >= 1:
+                layer.wait_host()
+        layer.wait_host()
+        tif_s = (time.perf_counter() - t0) / args.steps
+        two_in_flight = {"value": T / tif_s, "unit": UNIT, "ms_per_step": 1e3 * tif_s,
+                         "same_output": bool(torch.equal(hout, keep))}
+
     two_ctx = None
     if not w.streamed and not args.no_two_contexts:
         import threading
@@ -414,7 +438,7 @@ def run_single(args, w):
         "config": dict(workload_config(w, 1), **({"expert_cache_slots": args.cache_slots} if args.cache_slots else {})),
         "e2e": {"value": T / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(hx.numel() * 4),
                 "d2h_bytes_per_step": int(hout.numel() * 4), "ms_per_step": 1e3 * e2e_s,
-                "two_contexts": two_ctx},
+                "two_in_flight": two_in_flight, "two_contexts": two_ctx},
         "gpu_launches": int(launches), "stage_ms": stage_ms, "active_experts": active,
         "ffn_useful_tflops": 6.0 * T * D * F / ((stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) * 1e-3) / 1e12
         if (stage_ms["ffn_gemm1"] + stage_ms["ffn_gemm2"]) > 0 else None,

@@ -155,6 +155,14 @@ INFMOE_API int infmoe_layer_sync_status(infmoe_layer* layer, void* stream);
  * is the end-to-end call the benchmark times. */
 INFMOE_API int infmoe_layer_forward_host(infmoe_layer* layer, const float* h_input, float* h_output,
                                          int64_t token_num);
+/* The same without waiting (no reference counterpart): the step's upload, pass and result transfer are enqueued and
+ * the call returns; infmoe_layer_wait_host blocks until the OLDEST submitted step's result is in its h_output and
+ * returns that step's status.  At most two steps may be in flight: the upload of one then runs behind the pass of
+ * the one before.  Buffers should be page-locked (the result is then written into h_output by the last kernel of the
+ * pass itself) and must stay untouched until the step has been waited for.  infmoe_layer_forward_host refuses to
+ * run while steps are in flight. */
+INFMOE_API int infmoe_layer_submit_host(infmoe_layer* layer, const float* h_input, float* h_output, int64_t token_num);
+INFMOE_API int infmoe_layer_wait_host(infmoe_layer* layer);
 
 /* Routing/dispatch results of the last enqueue (device pointers inside the
  * workspace of that call; valid until the next enqueue).  Any out pointer may be NULL. */

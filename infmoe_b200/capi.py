@@ -111,6 +111,8 @@ SIGNATURES = {
     "infmoe_layer_expert_forward_scatter": [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i64, _vp],
     "infmoe_layer_sync_status": [_vp, _vp],
     "infmoe_layer_forward_host": [_vp, _vp, _vp, _i64],
+    "infmoe_layer_submit_host": [_vp, _vp, _vp, _i64],
+    "infmoe_layer_wait_host": [_vp],
     "infmoe_layer_last_routing": [_vp] + [ctypes.POINTER(_vp)] * 5,
     "infmoe_layer_kernel_launches": [_vp],
     "infmoe_layer_set_profiling": [_vp, ctypes.c_int],

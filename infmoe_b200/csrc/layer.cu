@@ -167,6 +167,15 @@ struct infmoe_layer {
     float* own_out = nullptr;
     void* own_ws = nullptr;
     size_t own_io_bytes = 0, own_ws_bytes = 0;
+    // two host-buffer steps in flight (infmoe_layer_submit_host / _wait_host)
+    float* pipe_in[2] = {nullptr, nullptr};
+    float* pipe_out[2] = {nullptr, nullptr};
+    size_t pipe_io_bytes = 0;
+    cudaStream_t pipe_in_stream = nullptr, pipe_out_stream = nullptr;
+    cudaEvent_t pipe_ev_in[2] = {nullptr, nullptr}, pipe_ev_pass[2] = {nullptr, nullptr}, pipe_ev_out[2] = {nullptr, nullptr};
+    bool pipe_used[2] = {false, false};
+    int* pipe_h_status = nullptr;        // pinned [2]
+    long long pipe_submitted = 0, pipe_waited = 0;
     cudaStream_t own_stream = nullptr;
 
     // Optional expert cache of the streamed mode (no counterpart in the reference, whose slots forget their
@@ -440,6 +449,21 @@ void free_device_state(infmoe_layer* L) {
     if (L->own_in) cudaFree(L->own_in);
     if (L->own_out) cudaFree(L->own_out);
     if (L->own_ws) cudaFree(L->own_ws);
+    for (int i = 0; i < 2; ++i) {
+        if (L->pipe_in[i]) cudaFree(L->pipe_in[i]);
+        if (L->pipe_out[i]) cudaFree(L->pipe_out[i]);
+        for (cudaEvent_t e : {L->pipe_ev_in[i], L->pipe_ev_pass[i], L->pipe_ev_out[i]})
+            if (e) cudaEventDestroy(e);
+        L->pipe_in[i] = L->pipe_out[i] = nullptr;
+        L->pipe_ev_in[i] = L->pipe_ev_pass[i] = L->pipe_ev_out[i] = nullptr;
+        L->pipe_used[i] = false;
+    }
+    L->pipe_io_bytes = 0;
+    if (L->pipe_h_status) cudaFreeHost(L->pipe_h_status);
+    L->pipe_h_status = nullptr;
+    if (L->pipe_in_stream) cudaStreamDestroy(L->pipe_in_stream);
+    if (L->pipe_out_stream) cudaStreamDestroy(L->pipe_out_stream);
+    L->pipe_in_stream = L->pipe_out_stream = nullptr;
     if (L->own_stream) cudaStreamDestroy(L->own_stream);
 }
 
@@ -1277,6 +1301,10 @@ int infmoe_layer_forward_host(infmoe_layer* L, const float* h_in, float* h_out, 
         set_error("layer_forward_host: bad argument");
         return INFMOE_ERR_INVALID_ARGUMENT;
     }
+    if (L->pipe_submitted != L->pipe_waited) {
+        set_error("layer_forward_host: steps submitted with infmoe_layer_submit_host are still in flight");
+        return INFMOE_ERR_STATE;
+    }
     if (T == 0) return INFMOE_OK;
     if (!L->own_stream) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking));
     const size_t io = sizeof(float) * (size_t)T * L->D;
@@ -1317,6 +1345,111 @@ int infmoe_layer_forward_host(infmoe_layer* L, const float* h_in, float* h_out, 
                                     L->own_stream));
     if (!direct) INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, L->own_out, io, cudaMemcpyDeviceToHost, L->own_stream));
     return infmoe_layer_sync_status(L, L->own_stream);
+}
+
+// Host buffers in and out without waiting: at most two steps in flight.  The upload of a step runs on a copy stream
+// behind the pass of the step before; the result goes straight into a page-locked h_out from the last kernel of the
+// pass, or through a device buffer and a copy on a third stream into a pageable one.
+int infmoe_layer_submit_host(infmoe_layer* L, const float* h_in, float* h_out, int64_t T) {
+    if (!L || T <= 0 || !h_in || !h_out) {
+        set_error("layer_submit_host: bad argument");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (L->pipe_submitted - L->pipe_waited >= 2) {
+        set_error("layer_submit_host: two steps are in flight already; call infmoe_layer_wait_host first");
+        return INFMOE_ERR_STATE;
+    }
+    const size_t io = sizeof(float) * (size_t)T * L->D;
+    if (!L->own_stream) INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking));
+    if (!L->pipe_in_stream) {
+        INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&L->pipe_in_stream, cudaStreamNonBlocking));
+        INFMOE_CUDA_TRY(cudaStreamCreateWithFlags(&L->pipe_out_stream, cudaStreamNonBlocking));
+        INFMOE_CUDA_TRY(cudaHostAlloc(&L->pipe_h_status, 2 * sizeof(int), cudaHostAllocDefault));
+        L->pipe_h_status[0] = L->pipe_h_status[1] = 0;
+        for (int i = 0; i < 2; ++i)
+            for (cudaEvent_t* e : {&L->pipe_ev_in[i], &L->pipe_ev_pass[i], &L->pipe_ev_out[i]})
+                INFMOE_CUDA_TRY(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+    }
+    if (io > L->pipe_io_bytes) {
+        if (L->pipe_submitted != L->pipe_waited) {
+            set_error("layer_submit_host: a larger step cannot be submitted while a smaller one is in flight");
+            return INFMOE_ERR_STATE;
+        }
+        for (int i = 0; i < 2; ++i) {
+            if (L->pipe_in[i]) cudaFree(L->pipe_in[i]);
+            if (L->pipe_out[i]) cudaFree(L->pipe_out[i]);
+            L->pipe_in[i] = L->pipe_out[i] = nullptr;
+            L->pipe_used[i] = false;
+        }
+        L->pipe_io_bytes = 0;
+        for (int i = 0; i < 2; ++i) {
+            INFMOE_CUDA_TRY(cudaMalloc(&L->pipe_in[i], io));
+            INFMOE_CUDA_TRY(cudaMalloc(&L->pipe_out[i], io));
+        }
+        L->pipe_io_bytes = io;
+    }
+    size_t need = 0;
+    INFMOE_TRY(infmoe_layer_workspace_bytes(L, T, &need));
+    if (need > L->own_ws_bytes) {
+        INFMOE_CUDA_TRY(cudaStreamSynchronize(L->own_stream));   // a pass in flight may still use the old block
+        if (L->own_ws) cudaFree(L->own_ws);
+        L->own_ws = nullptr;
+        L->own_ws_bytes = 0;
+        INFMOE_CUDA_TRY(cudaMalloc(&L->own_ws, need));
+        L->own_ws_bytes = need;
+    }
+    const int s = (int)(L->pipe_submitted & 1);
+    cudaStream_t main = L->own_stream;
+    // upload: the staging buffer is free once the pass that read it last is done (the second GEMM reads its
+    // residual from the input)
+    if (L->pipe_used[s]) INFMOE_CUDA_TRY(cudaStreamWaitEvent(L->pipe_in_stream, L->pipe_ev_pass[s], 0));
+    INFMOE_CUDA_TRY(cudaMemcpyAsync(L->pipe_in[s], h_in, io, cudaMemcpyHostToDevice, L->pipe_in_stream));
+    INFMOE_CUDA_TRY(cudaEventRecord(L->pipe_ev_in[s], L->pipe_in_stream));
+    INFMOE_CUDA_TRY(cudaStreamWaitEvent(main, L->pipe_ev_in[s], 0));
+    float* direct = nullptr;
+    static const bool allow_direct = [] {
+        const char* v = getenv("INFMOE_DIRECT_HOST_OUTPUT");
+        return !(v && atoi(v) == 0);
+    }();
+    if (allow_direct && !L->identity && uses_umma(L)) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, h_out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+            direct = (float*)attr.devicePointer;
+        else
+            (void)cudaGetLastError();
+    }
+    // the device output buffer of this slot has been copied out
+    if (!direct && L->pipe_used[s]) INFMOE_CUDA_TRY(cudaStreamWaitEvent(main, L->pipe_ev_out[s], 0));
+    INFMOE_TRY(infmoe_layer_enqueue(L, L->pipe_in[s], direct ? direct : L->pipe_out[s], L->own_ws, L->own_ws_bytes, T, main));
+    INFMOE_TRY(layer_snapshot_status(L, L->pipe_h_status + s, main));
+    INFMOE_CUDA_TRY(cudaEventRecord(L->pipe_ev_pass[s], main));
+    if (direct) {
+        INFMOE_CUDA_TRY(cudaEventRecord(L->pipe_ev_out[s], main));
+    } else {
+        INFMOE_CUDA_TRY(cudaStreamWaitEvent(L->pipe_out_stream, L->pipe_ev_pass[s], 0));
+        INFMOE_CUDA_TRY(cudaMemcpyAsync(h_out, L->pipe_out[s], io, cudaMemcpyDeviceToHost, L->pipe_out_stream));
+        INFMOE_CUDA_TRY(cudaEventRecord(L->pipe_ev_out[s], L->pipe_out_stream));
+    }
+    L->pipe_used[s] = true;
+    L->pipe_submitted++;
+    return INFMOE_OK;
+}
+
+int infmoe_layer_wait_host(infmoe_layer* L) {
+    if (!L) {
+        set_error("layer_wait_host: null layer");
+        return INFMOE_ERR_INVALID_ARGUMENT;
+    }
+    if (L->pipe_waited == L->pipe_submitted) {
+        set_error("layer_wait_host: nothing in flight");
+        return INFMOE_ERR_STATE;
+    }
+    const int s = (int)(L->pipe_waited & 1);
+    INFMOE_CUDA_TRY(cudaEventSynchronize(L->pipe_ev_out[s]));
+    L->pipe_waited++;
+    const int st = L->pipe_h_status[s];
+    L->pipe_h_status[s] = 0;
+    return status_to_rc(st);
 }
 
 int infmoe_layer_last_routing(const infmoe_layer* L, const int32_t** gate, const float** score, const int32_t** pos,

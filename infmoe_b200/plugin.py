@@ -314,6 +314,14 @@ class MoELayer:
     def forward_host_ptr(self, h_in: int, h_out: int, token_num: int) -> None:
         capi.check(capi.lib().infmoe_layer_forward_host(self._h, h_in, h_out, int(token_num)))
 
+    def submit_host_ptr(self, h_in: int, h_out: int, token_num: int) -> None:
+        """Enqueues a step with host buffers and returns; at most two steps in flight (see wait_host)."""
+        capi.check(capi.lib().infmoe_layer_submit_host(self._h, h_in, h_out, int(token_num)))
+
+    def wait_host(self) -> None:
+        """Blocks until the oldest submitted step's result is in its output buffer; raises on its status."""
+        capi.check(capi.lib().infmoe_layer_wait_host(self._h))
+
     def set_profiling(self, enable: bool) -> None:
         capi.check(capi.lib().infmoe_layer_set_profiling(self._h, 1 if enable else 0))
 

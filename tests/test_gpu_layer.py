@@ -183,6 +183,49 @@ def test_forward_host_into_page_locked_output(torch_cuda, oracle, variant):
     layer.terminate()
 
 
+@pytest.mark.parametrize("pinned", [True, False])
+def test_two_host_steps_in_flight_give_the_bits_of_the_blocking_call(torch_cuda, oracle, pinned):
+    """infmoe_layer_submit_host / _wait_host: step k brings the rows rolled by k, two steps in flight; page-locked
+    buffers are written by the pass itself, pageable ones through a device buffer and a copy stream.  A NaN row is
+    reported by the wait of its own step only."""
+    from infmoe_b200 import capi, synth
+    torch = torch_cuda
+    w = synth.scaled(synth.WORKLOADS["cpm2"], variant="cpm_2", expert_count=6, embedding_size=128, hidden_size=256,
+                     batch=1, seq_len=200)
+    layer, x, c, ln, experts = _build(w, synth, from_npz=False)
+    want = torch.from_numpy(_check(layer, w, x, c, ln, experts, oracle, torch))
+    hx = torch.from_numpy(x)
+    mem = (lambda t: t.pin_memory()) if pinned else (lambda t: t.clone())
+    steps = 5
+    ins = [mem(torch.roll(hx, k, 0).contiguous()) for k in range(steps)]
+    ins[3][7, :] = float("nan")                                   # step 3 has a token without an expert
+    outs = [mem(torch.full_like(hx, float("nan"))) for _ in range(steps)]
+    status = []
+    for k in range(steps):
+        layer.submit_host_ptr(ins[k].data_ptr(), outs[k].data_ptr(), w.tokens)
+        if k >= 1:
+            try:
+                layer.wait_host()
+                status.append(0)
+            except capi.InfMoEError as e:
+                status.append(e.status)
+    with pytest.raises(capi.InfMoEError):                         # the blocking call is refused while a step is in flight
+        layer.forward_host_ptr(ins[0].data_ptr(), outs[0].data_ptr(), w.tokens)
+    layer.wait_host()
+    status.append(0)
+    with pytest.raises(capi.InfMoEError):                         # nothing left to wait for
+        layer.wait_host()
+    assert status == [0, 0, 0, 3, 0]
+    for k in range(steps):
+        got, exp = outs[k], torch.roll(want, k, 0)
+        if k == 3:                                                # the NaN token's row is left alone
+            keep = torch.ones(w.tokens, dtype=torch.bool)
+            keep[7] = False
+            got, exp = got[keep], exp[keep]
+        assert torch.equal(got, exp), k
+    layer.terminate()
+
+
 def test_bounded_wait_runs_out_and_leaves_the_context_usable(torch_cuda, oracle, tmp_path):
     """The wait every role of the expert GEMM uses, pointed at a barrier nothing completes, with a 50 ms limit:
     it gives up, raises the status bit and returns; the next layer call on the same context works."""
