@@ -160,7 +160,9 @@ INFMOE_API int infmoe_layer_forward_host(infmoe_layer* layer, const float* h_inp
  * returns that step's status.  At most two steps may be in flight: the upload of one then runs behind the pass of
  * the one before.  Buffers should be page-locked (the result is then written into h_output by the last kernel of the
  * pass itself) and must stay untouched until the step has been waited for.  infmoe_layer_forward_host refuses to
- * run while steps are in flight. */
+ * run while steps are in flight.  With streamed experts a pass waits for its weight copies on the host: submit then
+ * takes as long as the pass, and a token without an expert is reported by submit itself (the step is not in flight
+ * afterwards). */
 INFMOE_API int infmoe_layer_submit_host(infmoe_layer* layer, const float* h_input, float* h_output, int64_t token_num);
 INFMOE_API int infmoe_layer_wait_host(infmoe_layer* layer);
 
